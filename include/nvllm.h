@@ -488,6 +488,68 @@ int nvllm_gated_group_norm(void* out, int64_t ldo, const float* y, int64_t ldy, 
                            int32_t n, int32_t cols, int32_t parts, float eps, int32_t gate_first, int32_t out_dtype,
                            void* stream);
 
+/* ---- Sandwich RMS norms, windowed attention with sinks, latent attention in a window, the gated delta rule --------- */
+
+/* rms(v) = v / sqrt(mean(v^2) + eps).   y != NULL: h += rms(y) * post_w;   out != NULL: out = rms(h) * pre_w.
+ * h: f32 [n, hidden], updated in place; y in y_dtype, out in out_dtype; weights f32.  hidden <= 49152. */
+int nvllm_rms_residual_norm(void* out, float* h, const void* y, int32_t y_dtype, const float* post_w, const float* pre_w,
+                            int32_t n, int32_t hidden, float eps, int32_t out_dtype, void* stream);
+/* out[row_map ? row_map[i] : i, :cols] = rms(x[i, :cols]) * w (w nullable: 1); rows whose map entry is < 0 are skipped
+ * (the map is a paged cache's slot list, or NULL for row i -> row i).  x f32, out in out_dtype. */
+int nvllm_rms_norm_rows(void* out, int64_t ldo, const float* x, int64_t ldx, const float* w, const int32_t* row_map, int32_t n,
+                        int32_t cols, float eps, int32_t out_dtype, void* stream);
+/* h[t, :] = table[ids[t], :] * scale + bigram[r, :] as f32, r = (ids[t-1] * mul_prev + ids[t] * mul_cur) mod buckets, or
+ * r = buckets (the table's last row) where positions[t] == 0.  For the first token of a portion (cu_tokens) ids[t-1] is
+ * last_token[seq_slot[sequence]], which is then set to the portion's last token.  Padding sequences (slot < 0): zeros. */
+int nvllm_embedding_bigram(float* h, const void* table, const void* bigram, const int64_t* ids, const int64_t* positions,
+                           const int32_t* tok_seq, const int32_t* cu_tokens, const int32_t* seq_slot, int32_t* last_token,
+                           int32_t n, int32_t hidden, int32_t vocab, int32_t buckets, int32_t mul_prev, int32_t mul_cur, float scale,
+                           int32_t table_dtype, void* stream);
+/* Attention preparation with rotary positions.  proj: f32 [n, ...] rows [q (heads x dim) | k (kv_heads x dim) | v (kv_heads x
+ * vdim, absent with v_from_k) | ...].  Adds the biases (nullable); rotates the pairs (2i, 2i+1) of the first rot_dims values
+ * of every query and key head (table as nvllm_rope_table_interleaved builds); norm_eps > 0: divides each rotated head by
+ * its root mean square (eps inside the root, no weight); writes q in `dtype` and k / v into cache rows slots[i] (slot < 0:
+ * nothing stored).  v_from_k != 0: the values are the keys as projected (bias added, not rotated, not normed); vdim == dim. */
+int nvllm_attn_rope_norm_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row,
+                               const float* proj, int64_t ldp, const float* q_bias, const float* k_bias, const float* v_bias,
+                               const int64_t* positions, const float* rope_table, int32_t rot_dims, int32_t max_pos,
+                               float norm_eps, const int32_t* slots, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
+                               int32_t vdim, int32_t v_from_k, int32_t dtype, void* stream);
+/* nvllm_capped_attention with three more options: window > 0: position p sees only the keys p - window + 1 .. p;
+ * sinks (f32 [heads], nullable): exp(sinks[h]) joins the softmax denominator (unscaled, no value);
+ * gate_per_head != 0: gate is [n, heads] (ldg apart) and head h's output is multiplied by sigmoid(gate[t, h]). */
+int nvllm_window_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
+                           int32_t gate_per_head, const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
+                           const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables, int32_t table_cap,
+                           int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, float scale,
+                           float softcap, float temp_coef, int32_t temp_every, int32_t window, const float* sinks,
+                           const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream);
+/* nvllm_latent_attention with a sliding window (window > 0: keys p - window + 1 .. p), sinks (f32 [heads], nullable, as
+ * above) and a gate per head (f32 [n, heads], ldg apart, nullable: out[t, h, :] *= sigmoid(gate[t, h])). */
+int nvllm_latent_window_attention(void* out, int64_t ldo, const float* q_abs, int64_t ldqa, const void* q, int64_t ldq,
+                                  const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
+                                  int32_t table_cap, int32_t block_size, const void* cache, int64_t cache_row, int32_t n,
+                                  int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale, int32_t window,
+                                  const float* sinks, const float* gate, int64_t ldg, int32_t dtype, void* stream);
+/* Per-token preparation of the gated delta rule, in place, all f32:
+ *   q, k: [n, groups * dk] -> every head divided by sqrt(sum of squares + unit_eps), q also times q_scale;
+ *   beta: [n, heads] -> sigmoid;   decay: [n, heads * dk] -> exp(-exp(a_log[h]) * softplus(decay + dt_bias[h, c])). */
+int nvllm_delta_prepare(float* q, int64_t ldq, float* k, int64_t ldk, float* beta, int64_t ldb, float* decay, int64_t ldd,
+                        const float* a_log, const float* dt_bias, int32_t n, int32_t heads, int32_t groups, int32_t dk,
+                        float q_scale, float unit_eps, void* stream);
+/* Gated delta rule with a decay per key channel (sequence / slot conventions of nvllm_linear_recurrence), per head:
+ *   S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   y_t = S^T q_t        S: [dk, dv], state [slots, heads, dk, dv]
+ * q, k: [n, groups * dk]; v, y: [n, heads * dv]; decay g: [n, heads * dk]; beta: [n, heads].  dk <= 512.  All f32. */
+int nvllm_gated_delta_recurrence(float* y, int64_t ldy, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v,
+                                 int64_t ldv, const float* decay, int64_t ldd, const float* beta, int64_t ldb, float* state,
+                                 const int32_t* seq_slot, const int32_t* cu_tokens, const int64_t* positions, int32_t n_seqs,
+                                 int32_t heads, int32_t groups, int32_t dk, int32_t dv, void* stream);
+/* nvllm_gated_group_norm with the gate's activation as a parameter (gate_act 0: SiLU, 1: sigmoid) and, with w_shared != 0, one
+ * weight vector of cols / parts values used by every part. */
+int nvllm_gated_group_norm_act(void* out, int64_t ldo, const float* y, int64_t ldy, const float* gate, int64_t ldg, const float* w,
+                               int32_t w_shared, int32_t n, int32_t cols, int32_t parts, float eps, int32_t gate_first,
+                               int32_t gate_act, int32_t out_dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Engine-level C ABI: the C++ host runtime that mirrors the reference's Rust types one-to-one
  * (Config, SamplingParams, Sequence, BlockManager, Scheduler, ModelRunner, Qwen3Model, LLMEngine).

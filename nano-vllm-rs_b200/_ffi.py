@@ -105,6 +105,19 @@ PROTOTYPES = {
     "nvllm_moe_sort": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "nvllm_gemm_bf16_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, vp, vp]),
     "nvllm_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "nvllm_rms_residual_norm": (i32, [vp, vp, vp, i32, vp, vp, i32, i32, f32, i32, vp]),
+    "nvllm_rms_norm_rows": (i32, [vp, i64, vp, i64, vp, vp, i32, i32, f32, i32, vp]),
+    "nvllm_embedding_bigram": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]),
+    "nvllm_attn_rope_norm_store": (i32, [vp, i64, vp, vp, i64, i64, vp, i64, vp, vp, vp, vp, vp, i32, i32, f32, vp, i32, i32, i32, i32,
+                                         i32, i32, i32, vp]),
+    "nvllm_window_attention": (i32, [vp, i64, vp, i64, vp, i64, i32, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                     f32, f32, f32, i32, i32, vp, vp, i32, i32, vp]),
+    "nvllm_latent_window_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp, i64, i32, i32, i32, i32, i32, f32, i32,
+                                            vp, vp, i64, i32, vp]),
+    "nvllm_delta_prepare": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, i32, i32, i32, i32, f32, f32, vp]),
+    "nvllm_gated_delta_recurrence": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                                           vp]),
+    "nvllm_gated_group_norm_act": (i32, [vp, i64, vp, i64, vp, i64, vp, i32, i32, i32, i32, f32, i32, i32, i32, vp]),
 }
 
 

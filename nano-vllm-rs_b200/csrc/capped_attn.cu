@@ -2,12 +2,16 @@
 //   * no rotary: the only positional signal is a query temperature  1 + coef * ln(floor((p + 1) / every) + 1),
 //   * a soft cap on the scores:  s <- cap * tanh(s / cap)   (cap <= 0: none),
 //   * an optional output gate:   out *= sigmoid(gate)       (gate: f32 pre-activations, same layout as the output),
-//   * key and value sizes that may differ (dim, vdim).
+//   * key and value sizes that may differ (dim, vdim),
+//   * an optional sliding window: position p sees the keys p - window + 1 .. p   (window <= 0: all keys 0 .. p),
+//   * optional sinks: a learned number per head whose exponential joins the softmax denominator (no key, no value),
+//   * the gate as one number per head instead of one per output value.
 // Every query token carries its sequence (a row of the block tables) and its position, so one launch serves whole prompts,
 // portions of prompts and single decoded tokens side by side; position p sees the keys 0..p of its sequence.
 //
 // nvllm_attn_bias_store: the step before it — adds the projection biases, writes the queries in the operand type and the
-// keys / values into their cache rows.
+// keys / values into their cache rows.  nvllm_attn_rope_norm_store: the same step for layers with rotary positions on pairs
+// of neighbouring dimensions, a weightless per-head RMS norm after the rotation, and values that are the un-rotated keys.
 // Scores, softmax and the accumulation of P.V are f32.
 #include "common.cuh"
 
@@ -36,6 +40,72 @@ __global__ void attn_bias_store_kernel(T* __restrict__ q, int64_t ldq, T* __rest
   for (int c = threadIdx.x; c < vn; c += blockDim.x) stv(vc + slot * v_row + c, p[qn + kn + c] + (vb ? vb[c] : 0.f));
 }
 
+struct RopeStoreArgs {
+  void* q; int64_t ldq;
+  void *kc, *vc; int64_t k_row, v_row;
+  const float* proj; int64_t ldp;
+  const float *qb, *kb, *vb;
+  const int64_t* positions; const float2* table; int rot_dims, max_pos;
+  float norm_eps;
+  const int32_t* slots;
+  int n, heads, kv_heads, dim, vdim, v_from_k;
+};
+
+// One warp per (token, head) over the heads [q heads | key heads | value heads].  A query or key head: bias, rotation of the
+// pairs (2i, 2i+1) of its first rot_dims values by position * base^(-2i/rot_dims), then (norm_eps > 0) division by the root
+// mean square of the whole head; queries go to q, keys to their cache row.  A value head: bias, then its cache row; with
+// v_from_k the value head IS the key head as projected (bias added, neither rotated nor normed).
+template <typename T>
+__global__ void __launch_bounds__(128) attn_rope_norm_store_kernel(const RopeStoreArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = a.heads + a.kv_heads + (a.v_from_k ? 0 : a.kv_heads);
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  if (item >= static_cast<int64_t>(a.n) * per) return;
+  const int t = static_cast<int>(item / per), hh = static_cast<int>(item % per);
+  const float* p = a.proj + static_cast<int64_t>(t) * a.ldp;
+  const int32_t slot = a.slots[t];
+  const int qn = a.heads * a.dim, kn = a.kv_heads * a.dim;
+  if (hh >= a.heads + a.kv_heads) {   // a value head with columns of its own
+    if (slot < 0) return;
+    const int g = hh - a.heads - a.kv_heads;
+    T* dst = static_cast<T*>(a.vc) + static_cast<int64_t>(slot) * a.v_row + static_cast<int64_t>(g) * a.vdim;
+    for (int c = lane; c < a.vdim; c += 32) stv(dst + c, p[qn + kn + g * a.vdim + c] + (a.vb ? a.vb[g * a.vdim + c] : 0.f));
+    return;
+  }
+  const bool is_q = hh < a.heads;
+  const int h = is_q ? hh : hh - a.heads;
+  if (!is_q && slot < 0) return;
+  const float* src = p + (is_q ? 0 : qn) + static_cast<int64_t>(h) * a.dim;
+  const float* bias = is_q ? a.qb : a.kb;
+  if (bias) bias += static_cast<int64_t>(h) * a.dim;
+  if (!is_q && a.v_from_k) {
+    T* vd = static_cast<T*>(a.vc) + static_cast<int64_t>(slot) * a.v_row + static_cast<int64_t>(h) * a.vdim;
+    for (int c = lane; c < a.dim; c += 32) stv(vd + c, src[c] + (bias ? bias[c] : 0.f));
+  }
+  int64_t pos = a.positions[t];
+  pos = pos < 0 ? 0 : (pos >= a.max_pos ? a.max_pos - 1 : pos);
+  const float2* tab = a.table + pos * (a.rot_dims / 2);
+  T* dst = is_q ? static_cast<T*>(a.q) + static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(h) * a.dim
+                : static_cast<T*>(a.kc) + static_cast<int64_t>(slot) * a.k_row + static_cast<int64_t>(h) * a.dim;
+  // two passes over the head (sum of squares, then the store); the rotation is recomputed, nothing is staged
+  auto value = [&](int c) {
+    float v = src[c] + (bias ? bias[c] : 0.f);
+    if (c < a.rot_dims) {
+      const float o = src[c ^ 1] + (bias ? bias[c ^ 1] : 0.f);
+      const float2 cs = tab[c >> 1];
+      v = (c & 1) ? fmaf(v, cs.x, o * cs.y) : fmaf(v, cs.x, -o * cs.y);   // (u cos - v sin, v cos + u sin)
+    }
+    return v;
+  };
+  float r = 1.0f;
+  if (a.norm_eps > 0.f) {
+    float sq = 0.f;
+    for (int c = lane; c < a.dim; c += 32) { const float v = value(c); sq = fmaf(v, v, sq); }
+    r = 1.0f / sqrtf(warp_sum(sq) / a.dim + a.norm_eps);
+  }
+  for (int c = lane; c < a.dim; c += 32) stv(dst + c, value(c) * r);
+}
+
 struct AttnArgs {
   void* out; int64_t ldo;
   const void* q; int64_t ldq;
@@ -44,6 +114,7 @@ struct AttnArgs {
   const int32_t* tok_seq; const int64_t* positions; const int32_t* tables;
   int table_cap, block_size, n, heads, kv_heads, dim, vdim;
   float scale, softcap, temp_coef; int temp_every;
+  int window; const float* sinks; int gate_per_head;
 };
 
 constexpr int kMaxVPerLane = 16;  // vdim <= 512
@@ -72,11 +143,12 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
 #pragma unroll
   for (int i = 0; i < kMaxVPerLane; ++i) acc[i] = 0.f;
   const int nkeys = static_cast<int>(pos) + 1;
-  for (int j0 = 0; j0 < nkeys; j0 += 32) {
+  const int first = a.window > 0 ? max(0, nkeys - a.window) : 0;   // passes start at multiples of 32 whatever the window
+  for (int j0 = first & ~31; j0 < nkeys; j0 += 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
     int64_t slot = -1;
-    if (j < nkeys) {
+    if (j < nkeys && j >= first) {
       const int32_t blk = table[j / a.block_size];
       if (blk >= 0) {
         slot = static_cast<int64_t>(blk) * a.block_size + j % a.block_size;
@@ -108,15 +180,21 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
       }
     }
   }
+  if (a.sinks) {   // the sink joins the denominator only
+    const float sk = a.sinks[h], mn = fmaxf(m, sk), corr = expf(m - mn);
+    l = l * corr + expf(sk - mn);
+#pragma unroll
+    for (int i = 0; i < kMaxVPerLane; ++i) acc[i] *= corr;
+  }
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   T* o = static_cast<T*>(a.out) + t * a.ldo + static_cast<int64_t>(h) * a.vdim;
-  const float* gt = a.gate ? a.gate + t * a.ldg + static_cast<int64_t>(h) * a.vdim : nullptr;
+  const float* gt = a.gate ? a.gate + t * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim) : nullptr;
 #pragma unroll
   for (int i = 0; i < kMaxVPerLane; ++i) {
     const int c = lane + 32 * i;
     if (c < a.vdim) {
       float v = acc[i] * inv;
-      if (gt) v *= 1.0f / (1.0f + expf(-gt[c]));
+      if (gt) v *= 1.0f / (1.0f + expf(-gt[a.gate_per_head ? 0 : c]));
       stv(o + c, v);
     }
   }
@@ -144,8 +222,8 @@ __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2
 // O[:, 0 .. 16 VP) += P . V.  k_addr / v_addr are the warp's ldmatrix lane addresses of its first key (and first value column).
 template <int DMAX, int VMAX, int NP, int VP, int QS, int VS>
 __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2], float (&l)[2], uint32_t q_addr, uint32_t k_addr,
-                                          uint32_t v_addr, int key0, const int (&pos)[2], const float (&qscale)[2], bool capped, float cap2,
-                                          bool need_mask, int tq4) {
+                                          uint32_t v_addr, int key0, const int (&pos)[2], int back, const float (&qscale)[2],
+                                          bool capped, float cap2, bool need_mask, int tq4) {
   float s[2 * NP][4];
 #pragma unroll
   for (int i = 0; i < 2 * NP; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -169,7 +247,7 @@ __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2]
       const int i = e >> 1, j = key0 + nt * 8 + 2 * tq4 + (e & 1);
       float v = s[nt][e] * qscale[i];            // with a cap: the score over the cap; without: the score in log2 units
       if (capped) v = cap2 * fast_tanh(v);
-      if (need_mask) v = j <= pos[i] ? v : -INFINITY;
+      if (need_mask) v = (j <= pos[i] && j >= pos[i] - back) ? v : -INFINITY;   // back: window - 1, or no bound
       s[nt][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -278,6 +356,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   const bool few = ntok * group <= 16;
   const int rbase = few ? 0 : warp * 16, kq = warp & 3, vh = warp >> 2;
   int pos[2]; float qscale[2]; bool valid[2];
+  const int back = a.window > 0 ? a.window - 1 : (1 << 30);   // a row sees the keys pos - back .. pos
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = rbase + gq + 8 * i, t = r / group;
@@ -289,6 +368,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   // the smallest position of the warp's rows decides whether a tile needs the causal mask (empty rows count as hidden)
   const bool warp_has_rows = rbase / group < ntok;
   const int min_pos = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));
+  const int max_lo = __reduce_max_sync(0xffffffffu, max(pos[0], pos[1])) - back;   // a tile that starts before it needs the window's mask
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[VMAX / 8][4];
 #pragma unroll
@@ -296,13 +376,16 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   const bool capped = a.softcap > 0.f;
   const float cap2 = a.softcap * kLog2e;           // scores are kept in log2 units: softmax with exp2
   const int ntiles = (nkeys + kKeys - 1) / kKeys;
-  if (tid < kKeys) { slot_s[0][tid] = lookup(0); slot_s[1][tid] = lookup(1); }
+  // with a window the first tile is the one that holds the first key the CTA's first token sees (tiles stay anchored at
+  // multiples of 64 from the sequence's start)
+  const int kt0 = a.window > 0 ? max(0, static_cast<int>(a.positions[tok0]) - a.window + 1) / kKeys : 0;
+  if (tid < kKeys) { slot_s[kt0 & 1][tid] = lookup(kt0); slot_s[(kt0 + 1) & 1][tid] = lookup(kt0 + 1); }
   __syncthreads();
-  load_tile(0, 0);
+  load_tile(kt0, kt0 & 1);
   const uint32_t q_addr = smem_u32(Qs + (rbase + (lane & 15)) * QS + (lane >> 4) * 8);
   const int k_lane = ((lane & 7) + (lane >> 4) * 8) * QS + ((lane >> 3) & 1) * 8;
   const int v_lane = ((lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8;
-  for (int kt = 0; kt < ntiles; ++kt) {
+  for (int kt = kt0; kt < ntiles; ++kt) {
     const int buf = kt & 1;
     if (kt + 1 < ntiles) { load_tile(kt + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     const int64_t slot_ahead = (tid < kKeys && kt + 2 < ntiles) ? lookup(kt + 2) : -1;   // in flight during this tile's math
@@ -313,14 +396,15 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
       const int key0 = kt * kKeys + kq * 16;
       if (key0 < nkeys)
         attn_tile<DMAX, VMAX, 1, VMAX / 32, QS, VS>(o, m, l, q_addr, smem_u32(kb + kq * 16 * QS + k_lane),
-                                                    smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, qscale, capped, cap2,
-                                                    key0 + 15 > min_pos, tq4);
+                                                    smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, back, qscale, capped, cap2,
+                                                    key0 + 15 > min_pos || key0 < max_lo, tq4);
     } else if (warp_has_rows) {
       // two halves of 32 keys: half the score registers of a 64-key pass (no spills under the 128-register cap)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf)
         attn_tile<DMAX, VMAX, 2, VMAX / 16, QS, VS>(o, m, l, q_addr, smem_u32(kb + hf * 32 * QS + k_lane), smem_u32(vb + hf * 32 * VS + v_lane),
-                                                    kt * kKeys + hf * 32, pos, qscale, capped, cap2, kt * kKeys + hf * 32 + 31 > min_pos, tq4);
+                                                    kt * kKeys + hf * 32, pos, back, qscale, capped, cap2,
+                                                    kt * kKeys + hf * 32 + 31 > min_pos || kt * kKeys + hf * 32 < max_lo, tq4);
     }
     if (tid < kKeys) slot_s[kt & 1][tid] = slot_ahead;   // tile kt's slots were consumed by load_tile(kt) an iteration ago
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it
@@ -350,8 +434,13 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     const int rows = ntok * group;
     for (int e = tid; e < rows * a.vdim; e += kThreads) {
       const int r = e / a.vdim, c = e - r * a.vdim, t = r / group, h = g * group + r % group;
-      const float mm = fmaxf(fmaxf(ms[r], ms[16 + r]), fmaxf(ms[32 + r], ms[48 + r]));
+      float mm = fmaxf(fmaxf(ms[r], ms[16 + r]), fmaxf(ms[32 + r], ms[48 + r]));
       float num = 0.f, den = 0.f;
+      if (a.sinks) {   // the sink joins the denominator only (scores are in log2 units here)
+        const float sk = a.sinks[h] * kLog2e;
+        mm = fmaxf(mm, sk);
+        den = fast_exp2(sk - mm);
+      }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float w = fast_exp2(ms[k * 16 + r] - mm);     // a quarter that saw no key: exp2(-inf) = 0
@@ -359,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
         den = fmaf(w, ls[k * 16 + r], den);
       }
       float v = den > 0.f ? num / den : 0.f;
-      if (a.gate) v *= 1.0f / (1.0f + __expf(-a.gate[static_cast<int64_t>(tok0 + t) * a.ldg + static_cast<int64_t>(h) * a.vdim + c]));
+      if (a.gate) v *= 1.0f / (1.0f + __expf(-a.gate[static_cast<int64_t>(tok0 + t) * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim + c)]));
       static_cast<bf16*>(a.out)[static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim + c] = __float2bfloat16_rn(v);
     }
     return;
@@ -368,15 +457,22 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   for (int i = 0; i < 2; ++i) {
     if (!valid[i]) continue;
     const int r = warp * 16 + gq + 8 * i, t = r / group, h = g * group + r % group;
-    const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    float ll = l[i], oc = 1.0f;
+    if (a.sinks) {   // the sink joins the denominator only (scores are in log2 units here)
+      const float sk = a.sinks[h] * kLog2e, mn = fmaxf(m[i], sk);
+      oc = fast_exp2(m[i] - mn);
+      ll = ll * oc + fast_exp2(sk - mn);
+    }
+    const float inv = ll > 0.f ? oc / ll : 0.f;
     bf16* op = static_cast<bf16*>(a.out) + static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim;
-    const float* gt = a.gate ? a.gate + static_cast<int64_t>(tok0 + t) * a.ldg + static_cast<int64_t>(h) * a.vdim : nullptr;
+    const float* gt = a.gate ? a.gate + static_cast<int64_t>(tok0 + t) * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim) : nullptr;
+    const float gh = (gt && a.gate_per_head) ? 1.0f / (1.0f + __expf(-gt[0])) : 1.0f;
 #pragma unroll
     for (int vt = 0; vt < VMAX / 8; ++vt) {
       const int c = vt * 8 + 2 * tq4;
       if (c >= a.vdim) continue;
-      float v0 = o[vt][2 * i] * inv, v1 = o[vt][2 * i + 1] * inv;
-      if (gt) { v0 *= 1.0f / (1.0f + __expf(-gt[c])); v1 *= 1.0f / (1.0f + __expf(-gt[c + 1])); }
+      float v0 = o[vt][2 * i] * inv * gh, v1 = o[vt][2 * i + 1] * inv * gh;
+      if (gt && !a.gate_per_head) { v0 *= 1.0f / (1.0f + __expf(-gt[c])); v1 *= 1.0f / (1.0f + __expf(-gt[c + 1])); }
       *reinterpret_cast<uint32_t*>(op + c) = pack_bf16x2(v0, v1);
     }
   }
@@ -418,20 +514,58 @@ extern "C" int nvllm_attn_bias_store(void* q, int64_t ldq, void* k_cache, void* 
   return 0;
 }
 
+extern "C" int nvllm_attn_rope_norm_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row,
+                                          const float* proj, int64_t ldp, const float* q_bias, const float* k_bias,
+                                          const float* v_bias, const int64_t* positions, const float* rope_table, int32_t rot_dims,
+                                          int32_t max_pos, float norm_eps, const int32_t* slots, int32_t n, int32_t heads,
+                                          int32_t kv_heads, int32_t dim, int32_t vdim, int32_t v_from_k, int32_t dtype, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim &&
+                      max_pos > 0 && (!v_from_k || vdim == dim), NVLLM_ERR_ARG,
+                  "attn_rope_norm_store: heads=%d/%d dim=%d vdim=%d rot_dims=%d (even, <= dim; values from keys need vdim == dim)", heads,
+                  kv_heads, dim, vdim, rot_dims);
+  NVLLM_CHECK_ARG(ldq >= static_cast<int64_t>(heads) * dim && k_row >= static_cast<int64_t>(kv_heads) * dim &&
+                      v_row >= static_cast<int64_t>(kv_heads) * vdim &&
+                      ldp >= static_cast<int64_t>(heads + kv_heads) * dim + (v_from_k ? 0 : static_cast<int64_t>(kv_heads) * vdim),
+                  NVLLM_ERR_ARG, "attn_rope_norm_store: strides");
+  NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "attn_rope_norm_store: dtype %d", dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(q && k_cache && v_cache && proj && positions && slots && (rope_table || rot_dims == 0), NVLLM_ERR_ARG,
+                  "attn_rope_norm_store: NULL");
+  const RopeStoreArgs a{q, ldq, k_cache, v_cache, k_row, v_row, proj, ldp, q_bias, k_bias, v_bias, positions,
+                        reinterpret_cast<const float2*>(rope_table), rot_dims, max_pos, norm_eps, slots, n, heads, kv_heads, dim, vdim, v_from_k};
+  const int64_t items = static_cast<int64_t>(n) * (heads + kv_heads + (v_from_k ? 0 : kv_heads));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == NVLLM_BF16) attn_rope_norm_store_kernel<bf16><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);
+  else attn_rope_norm_store_kernel<float><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);
+  NVLLM_LAUNCH_CHECK("attn_rope_norm_store_kernel");
+  return 0;
+}
+
 extern "C" int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
                                       const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
                                       const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
                                       int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
                                       int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every,
                                       const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream) {
+  return nvllm_window_attention(out, ldo, q, ldq, gate, ldg, 0, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables, table_cap,
+                                block_size, n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, 0, nullptr, cu_tokens,
+                                n_seqs, dtype, stream);
+}
+
+extern "C" int nvllm_window_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
+                                      int32_t gate_per_head, const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
+                                      const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
+                                      int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
+                                      int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every, int32_t window,
+                                      const float* sinks, const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream) {
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && vdim <= 32 * kMaxVPerLane &&
                       dim <= 2048 && block_size > 0 && table_cap > 0 && temp_every > 0, NVLLM_ERR_ARG,
-                  "capped_attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 512)", n, heads, kv_heads, dim, vdim);
-  NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "capped_attention: dtype %d", dtype);
+                  "attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 512)", n, heads, kv_heads, dim, vdim);
+  NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "attention: dtype %d", dtype);
   if (n == 0) return 0;
-  NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && block_tables, NVLLM_ERR_ARG, "capped_attention: NULL");
+  NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && block_tables, NVLLM_ERR_ARG, "attention: NULL");
   AttnArgs a{out, ldo, q, ldq, gate, ldg, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables, table_cap, block_size,
-             n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every};
+             n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window > 0 ? window : 0, sinks, gate_per_head};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 with 16-byte rows and a token range per sequence: tensor cores; everything else (f32, odd sizes): one warp per row
   const int group = heads / kv_heads;

@@ -12,6 +12,9 @@
 // on the shared key part and on the queries' rotated part, store into the paged cache) and the paged attention itself, which
 // takes every query token with its own sequence index and position — prompt portions, single decoded tokens and any mix of
 // them are one launch.  Softmax, norms and all accumulation are f32; cache and activations are bf16 or f32 (dtype).
+// Options of the attention (nvllm_latent_window_attention): a sliding window (position p sees p - window + 1 .. p), a sink
+// per head whose exponential joins the softmax denominator, and a gate per head (out *= sigmoid(gate)); the rotated part
+// may be absent (rot_dim = 0).
 #include "common.cuh"
 
 namespace nvllm {
@@ -95,6 +98,7 @@ struct AttnArgs {
   const void* cache; int64_t cache_row;
   int n, heads, dim, rot_dim, kv_rank;
   float scale;
+  int window; const float* sinks; const float* gate; int64_t ldg;   // 0 / null: none
 };
 
 constexpr int kKeyTile = 32;
@@ -123,7 +127,8 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const AttnArgs a) {
 #pragma unroll
   for (int i = 0; i < RI; ++i) acc[i] = 0.f;
   const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
-  for (int j0 = 0; j0 < nkeys; j0 += kKeyTile) {
+  const int first = a.window > 0 ? max(0, nkeys - a.window) : 0;   // tiles start at multiples of kKeyTile whatever the window
+  for (int j0 = first & ~(kKeyTile - 1); j0 < nkeys; j0 += kKeyTile) {
     const int cnt = min(kKeyTile, nkeys - j0);
     __syncthreads();
     for (int e = threadIdx.x; e < cnt * D; e += blockDim.x) {
@@ -137,7 +142,7 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const AttnArgs a) {
     __syncthreads();
     if (!active) continue;
     float s = -INFINITY;
-    if (lane < cnt && table[(j0 + lane) / a.block_size] >= 0) {
+    if (lane < cnt && j0 + lane >= first && table[(j0 + lane) / a.block_size] >= 0) {
       s = 0.f;
       const float* k = ks + lane * stride;
       const float* q = qs + warp * D;
@@ -161,7 +166,14 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const AttnArgs a) {
   }
   if (!active) return;
   T* o = static_cast<T*>(a.out) + static_cast<int64_t>(t) * a.ldo + static_cast<int64_t>(h) * a.kv_rank;
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  float oc = 1.0f;
+  if (a.sinks) {   // the sink joins the denominator only
+    const float sk = a.sinks[h], mn = fmaxf(m, sk);
+    oc = expf(m - mn);
+    l = l * oc + expf(sk - mn);
+  }
+  float inv = l > 0.f ? oc / l : 0.f;
+  if (a.gate) inv *= 1.0f / (1.0f + expf(-a.gate[static_cast<int64_t>(t) * a.ldg + h]));
 #pragma unroll
   for (int i = 0; i < RI; ++i)
     if (lane + 32 * i < a.kv_rank) stf(o + lane + 32 * i, acc[i] * inv);
@@ -228,7 +240,7 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
   const int npass = (TQ == 1 || together || tfirst + 1 >= a.n) ? 1 : 2;
   for (int pass = 0; pass < npass; ++pass) {
     // tokens of this pass: slot q holds token tq[q] (-1: slot unused)
-    int tq[TQ], nk[TQ], nkeys = 0;
+    int tq[TQ], nk[TQ], lo[TQ], nkeys = 0;
     const int t_lead = tfirst + pass;
     const int32_t* table = a.tables + static_cast<int64_t>(a.tok_seq[t_lead]) * a.table_cap;
 #pragma unroll
@@ -239,8 +251,14 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
     }
     for (int b = 0; b * a.block_size < nkeys; ++b)   // a missing block ends the sequence's keys (padding rows of a graph: none)
       if (table[b] < 0) { nkeys = b * a.block_size; break; }
+    int jstart = nkeys;
 #pragma unroll
-    for (int q = 0; q < TQ; ++q) nk[q] = nk[q] < nkeys ? nk[q] : nkeys;
+    for (int q = 0; q < TQ; ++q) {
+      lo[q] = a.window > 0 && nk[q] > a.window ? nk[q] - a.window : 0;   // first key the token sees (from its position alone)
+      nk[q] = nk[q] < nkeys ? nk[q] : nkeys;
+      if (tq[q] >= 0) jstart = lo[q] < jstart ? lo[q] : jstart;
+    }
+    jstart &= ~(kMmaKeys - 1);   // key tiles stay anchored at multiples of 64 from the sequence's start
     __syncthreads();   // previous pass done with every buffer; the zero fill above is ordered before the copies below
     if (tid < TQ * 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
     // four threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
@@ -257,7 +275,7 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
       for (int v = tid & 3; v < vec_per_row; v += 4) cp_async_16(dst + v * 16, src + (bytes ? v * 8 : 0), bytes);
       cp_async_commit();
     };
-    prefetch(0, Kbuf);
+    prefetch(jstart, Kbuf);
     // the queries: [folded q (f32 -> bf16) | rotated part | zeros up to the cache row's width]
 #pragma unroll
     for (int q = 0; q < TQ; ++q) {
@@ -293,7 +311,7 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
 #pragma unroll
       for (int i = 0; i < 2 * NT2; ++i) acc[q][i][0] = acc[q][i][1] = acc[q][i][2] = acc[q][i][3] = 0.f;
     int buf = 0;
-    for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys, buf ^= 1) {
+    for (int j0 = jstart; j0 < nkeys; j0 += kMmaKeys, buf ^= 1) {
       bf16* Ks = Kbuf + buf * kMmaKeys * DPS;
       if (j0 + kMmaKeys < nkeys) {
         prefetch(j0 + kMmaKeys, Kbuf + (buf ^ 1) * kMmaKeys * DPS);   // that buffer's last readers passed the barrier below
@@ -357,10 +375,11 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
         const int q = warp >> 2, row = 4 * (warp & 3) + (lane >> 3), sub = lane & 7;
         const float* S0 = Ss + q * 2 * 16 * kSsStride;
         const int nkq = (TQ == 1) ? nk[0] : (q == 0 ? nk[0] : nk[TQ - 1]);
+        const int loq = (TQ == 1) ? lo[0] : (q == 0 ? lo[0] : lo[TQ - 1]);
         float sv[8], mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const bool ok = j0 + sub * 8 + i < nkq;
+          const bool ok = j0 + sub * 8 + i < nkq && j0 + sub * 8 + i >= loq;
           sv[i] = ok ? (S0[row * kSsStride + sub * 8 + i] + S0[(16 + row) * kSsStride + sub * 8 + i]) * a.scale : -INFINITY;
           mx = fmaxf(mx, sv[i]);
         }
@@ -423,7 +442,14 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
       for (int half = 0; half < 2; ++half) {
         const int r = g + 8 * half, h = hbase + r;
         if (h >= a.heads) continue;
-        const float l = l_s[q * 16 + r], inv = l > 0.f ? 1.0f / l : 0.f;
+        float l = l_s[q * 16 + r], oc = 1.0f;
+        if (a.sinks) {   // the sink joins the denominator only
+          const float sk = a.sinks[h], mo = m_s[q * 16 + r], mn = fmaxf(mo, sk);
+          oc = expf(mo - mn);
+          l = l * oc + expf(sk - mn);
+        }
+        float inv = l > 0.f ? oc / l : 0.f;
+        if (a.gate) inv *= 1.0f / (1.0f + expf(-a.gate[static_cast<int64_t>(tq[q]) * a.ldg + h]));
 #pragma unroll
         for (int nt = 0; nt < 2 * NT2; ++nt)
 #pragma unroll
@@ -510,13 +536,23 @@ extern "C" int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs
                                       int32_t table_cap, int32_t block_size, const void* cache, int64_t cache_row, int32_t n,
                                       int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale,
                                       int32_t dtype, void* stream) {
+  return nvllm_latent_window_attention(out, ldo, q_abs, ldqa, q, ldq, tok_seq, positions, block_tables, table_cap, block_size, cache,
+                                       cache_row, n, heads, dim, rot_dim, kv_rank, scale, 0, nullptr, nullptr, 0, dtype, stream);
+}
+
+extern "C" int nvllm_latent_window_attention(void* out, int64_t ldo, const float* q_abs, int64_t ldqa, const void* q, int64_t ldq,
+                                             const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
+                                             int32_t table_cap, int32_t block_size, const void* cache, int64_t cache_row, int32_t n,
+                                             int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale,
+                                             int32_t window, const float* sinks, const float* gate, int64_t ldg, int32_t dtype,
+                                             void* stream) {
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && dim >= 0 && rot_dim >= 0 && kv_rank > 0 && kv_rank <= 1024 && table_cap > 0 && block_size > 0,
                   NVLLM_ERR_ARG, "latent_attention: sizes (kv_rank <= 1024)");
   NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "latent_attention: dtype %d", dtype);
   if (n == 0) return 0;
-  NVLLM_CHECK_ARG(out && q_abs && q && tok_seq && positions && block_tables && cache, NVLLM_ERR_ARG, "latent_attention: NULL");
-  const AttnArgs a{out, ldo, q_abs, ldqa, q, ldq, tok_seq, positions, block_tables, table_cap, block_size, cache, cache_row,
-                   n, heads, dim, rot_dim, kv_rank, scale};
+  NVLLM_CHECK_ARG(out && q_abs && (q || rot_dim == 0) && tok_seq && positions && block_tables && cache, NVLLM_ERR_ARG, "latent_attention: NULL");
+  const AttnArgs a{out, ldo, q_abs, ldqa, q ? q : q_abs, ldq, tok_seq, positions, block_tables, table_cap, block_size, cache, cache_row,
+                   n, heads, dim, rot_dim, kv_rank, scale, window > 0 ? window : 0, sinks, gate, ldg};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 caches with a 16-byte row pitch and kv_rank <= 512 run on the tensor cores (NVLLM_LATENT_MMA=0: the CUDA-core kernel)
   const int dp16 = (static_cast<int>(cache_row) + 15) / 16 * 16;

@@ -1,0 +1,185 @@
+// rms_norm.cu — RMS norms around an f32 residual stream, and an embedding with a hashed bigram term.
+//
+//   nvllm_rms_residual_norm   the fused step of a block with a norm before AND after every sublayer:
+//                                 h += rms(y) * post_w;   out = rms(h) * pre_w          rms(v) = v / sqrt(mean(v^2) + eps)
+//                             (the sublayer's output norm, the residual add and the next sublayer's input norm in one pass over
+//                             the row, as nvllm_dyt_residual_norm does for Dynamic Tanh models)
+//   nvllm_rms_norm_rows       rows of an f32 matrix, RMS-normed and weighted, written in the operand type to rows of a
+//                             destination chosen by a map (a paged cache's slots) or in place of order
+//   nvllm_embedding_bigram    h[t] = table[id_t] * scale + bigram[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]; the first
+//                             token of a sequence reads the extra row `buckets`.  The token before a portion's first one is
+//                             part of the sequence's state (one int32 per state slot).
+// Statistics, sums and the stream are f32; y / out / tables are bf16 or f32.
+#include "common.cuh"
+
+namespace nvllm {
+namespace {
+
+__device__ __forceinline__ float ld_any(const void* p, int dt, int64_t i) {
+  return dt == NVLLM_F32 ? static_cast<const float*>(p)[i] : __bfloat162float(static_cast<const bf16*>(p)[i]);
+}
+template <typename TO>
+__device__ __forceinline__ void st_as(TO* p, int64_t i, float v) {
+  if (sizeof(TO) == 2) reinterpret_cast<bf16*>(p)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(p)[i] = v;
+}
+
+// every thread returns the same sum (fixed order over the warps)
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// CTA per row; the row lives in shared memory between the passes.
+template <typename TO>
+__global__ void __launch_bounds__(256) rms_residual_norm_kernel(TO* __restrict__ out, float* __restrict__ h, const void* __restrict__ y, int y_dt,
+                                                                const float* __restrict__ post_w, const float* __restrict__ pre_w, int hidden,
+                                                                float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[8];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
+  float sq = 0.f;
+  if (y != nullptr) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = ld_any(y, y_dt, base + c);
+      row[c] = v;
+      sq = fmaf(v, v, sq);
+    }
+    const float r = 1.0f / sqrtf(block_sum(sq, red) / hidden + eps);
+    sq = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = h[base + c] + row[c] * r * post_w[c];
+      h[base + c] = v;
+      row[c] = v;
+      sq = fmaf(v, v, sq);
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = h[base + c];
+      row[c] = v;
+      sq = fmaf(v, v, sq);
+    }
+  }
+  if (out == nullptr) return;
+  const float r = 1.0f / sqrtf(block_sum(sq, red) / hidden + eps);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) st_as(out, base + c, row[c] * r * pre_w[c]);
+}
+
+// One warp per row.
+template <typename TO>
+__global__ void __launch_bounds__(128) rms_norm_rows_kernel(TO* __restrict__ out, int64_t ldo, const float* __restrict__ x, int64_t ldx,
+                                                            const float* __restrict__ w, const int32_t* __restrict__ row_map, int n, int cols,
+                                                            float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n) return;
+  const int64_t dst = row_map ? row_map[t] : t;
+  if (dst < 0) return;
+  const float* xr = x + static_cast<int64_t>(t) * ldx;
+  float sq = 0.f;
+  for (int c = lane; c < cols; c += 32) { const float v = xr[c]; sq = fmaf(v, v, sq); }
+  const float r = 1.0f / sqrtf(warp_sum(sq) / cols + eps);
+  for (int c = lane; c < cols; c += 32) st_as(out, dst * ldo + c, xr[c] * r * (w ? w[c] : 1.0f));
+}
+
+struct BigramArgs {
+  float* h;
+  const void *table, *bigram;
+  const int64_t *ids, *positions;
+  const int32_t *tok_seq, *cu_tokens, *seq_slot;
+  int32_t* last_token;
+  int hidden, vocab, buckets;
+  int64_t mul_prev, mul_cur;
+  float scale;
+};
+
+// CTA per token.  The thread block of a portion's FIRST token is the only one that touches the sequence's state word: it
+// reads the token before the portion and then stores the portion's last token.
+template <typename T>
+__global__ void __launch_bounds__(128) embedding_bigram_kernel(const BigramArgs a) {
+  const int t = blockIdx.x;
+  const int s = a.tok_seq[t], slot = a.seq_slot[s], c0 = a.cu_tokens[s];
+  float* hr = a.h + static_cast<int64_t>(t) * a.hidden;
+  if (slot < 0) {  // padding row of a captured batch
+    for (int c = threadIdx.x; c < a.hidden; c += blockDim.x) hr[c] = 0.f;
+    return;
+  }
+  int64_t id = a.ids[t];
+  id = id < 0 ? 0 : (id >= a.vocab ? a.vocab - 1 : id);
+  int64_t row = a.buckets;
+  if (a.positions[t] > 0) {
+    int64_t prev = t > c0 ? a.ids[t - 1] : a.last_token[slot];
+    prev = prev < 0 ? 0 : (prev >= a.vocab ? a.vocab - 1 : prev);
+    row = (prev * a.mul_prev + id * a.mul_cur) % a.buckets;
+  }
+  const T* e = static_cast<const T*>(a.table) + id * a.hidden;
+  const T* b = static_cast<const T*>(a.bigram) + row * a.hidden;
+  for (int c = threadIdx.x; c < a.hidden; c += blockDim.x) hr[c] = fmaf(ld_any(e, sizeof(T) == 2 ? NVLLM_BF16 : NVLLM_F32, c), a.scale,
+                                                                        ld_any(b, sizeof(T) == 2 ? NVLLM_BF16 : NVLLM_F32, c));
+  if (t == c0) {
+    __syncthreads();   // every thread of this block has read last_token[slot]
+    if (threadIdx.x == 0) a.last_token[slot] = static_cast<int32_t>(a.ids[a.cu_tokens[s + 1] - 1]);
+  }
+}
+
+}  // namespace
+}  // namespace nvllm
+
+using namespace nvllm;
+
+extern "C" int nvllm_rms_residual_norm(void* out, float* h, const void* y, int32_t y_dtype, const float* post_w, const float* pre_w,
+                                       int32_t n, int32_t hidden, float eps, int32_t out_dtype, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && hidden > 0 && hidden <= 48 * 1024, NVLLM_ERR_ARG, "rms_residual_norm: n=%d hidden=%d (<= 49152)", n, hidden);
+  NVLLM_CHECK_ARG((out_dtype == NVLLM_BF16 || out_dtype == NVLLM_F32) && (y_dtype == NVLLM_BF16 || y_dtype == NVLLM_F32), NVLLM_ERR_DTYPE,
+                  "rms_residual_norm: dtype %d / %d", y_dtype, out_dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(h && (out || y) && (!y || post_w) && (!out || pre_w), NVLLM_ERR_ARG, "rms_residual_norm: NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+  if (out_dtype == NVLLM_BF16) {
+    NVLLM_SMEM_ATTR_ONCE(rms_residual_norm_kernel<bf16>, 192 * 1024);
+    rms_residual_norm_kernel<bf16><<<n, 256, smem, st>>>(static_cast<bf16*>(out), h, y, y_dtype, post_w, pre_w, hidden, eps);
+  } else {
+    NVLLM_SMEM_ATTR_ONCE(rms_residual_norm_kernel<float>, 192 * 1024);
+    rms_residual_norm_kernel<float><<<n, 256, smem, st>>>(static_cast<float*>(out), h, y, y_dtype, post_w, pre_w, hidden, eps);
+  }
+  NVLLM_LAUNCH_CHECK("rms_residual_norm_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_rms_norm_rows(void* out, int64_t ldo, const float* x, int64_t ldx, const float* w, const int32_t* row_map, int32_t n,
+                                   int32_t cols, float eps, int32_t out_dtype, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && cols > 0 && ldo >= cols && ldx >= cols, NVLLM_ERR_ARG, "rms_norm_rows: n=%d cols=%d", n, cols);
+  NVLLM_CHECK_ARG(out_dtype == NVLLM_BF16 || out_dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "rms_norm_rows: dtype %d", out_dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(out && x, NVLLM_ERR_ARG, "rms_norm_rows: NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == NVLLM_BF16) rms_norm_rows_kernel<bf16><<<(n + 3) / 4, 128, 0, st>>>(static_cast<bf16*>(out), ldo, x, ldx, w, row_map, n, cols, eps);
+  else rms_norm_rows_kernel<float><<<(n + 3) / 4, 128, 0, st>>>(static_cast<float*>(out), ldo, x, ldx, w, row_map, n, cols, eps);
+  NVLLM_LAUNCH_CHECK("rms_norm_rows_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_embedding_bigram(float* h, const void* table, const void* bigram, const int64_t* ids, const int64_t* positions,
+                                      const int32_t* tok_seq, const int32_t* cu_tokens, const int32_t* seq_slot, int32_t* last_token,
+                                      int32_t n, int32_t hidden, int32_t vocab, int32_t buckets, int32_t mul_prev, int32_t mul_cur,
+                                      float scale, int32_t table_dtype, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && hidden > 0 && vocab > 0 && buckets > 0, NVLLM_ERR_ARG, "embedding_bigram: n=%d hidden=%d vocab=%d buckets=%d", n,
+                  hidden, vocab, buckets);
+  NVLLM_CHECK_ARG(table_dtype == NVLLM_BF16 || table_dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "embedding_bigram: dtype %d", table_dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(h && table && bigram && ids && positions && tok_seq && cu_tokens && seq_slot && last_token, NVLLM_ERR_ARG,
+                  "embedding_bigram: NULL");
+  const BigramArgs a{h, table, bigram, ids, positions, tok_seq, cu_tokens, seq_slot, last_token, hidden, vocab, buckets, mul_prev, mul_cur, scale};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (table_dtype == NVLLM_BF16) embedding_bigram_kernel<bf16><<<n, 128, 0, st>>>(a);
+  else embedding_bigram_kernel<float><<<n, 128, 0, st>>>(a);
+  NVLLM_LAUNCH_CHECK("embedding_bigram_kernel");
+  return 0;
+}
