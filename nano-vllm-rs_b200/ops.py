@@ -478,3 +478,97 @@ def gated_group_norm(y, gate, weight, parts, eps, gate_first, dtype):
     check(_ffi.lib().nvllm_gated_group_norm(_p(out), out.stride(0), _p(y), y.stride(0), _p(gate), gate.stride(0), _p(weight), n, cols,
                                             parts, eps, int(gate_first), _dt(out), _stream()))
     return out
+
+
+# (sandwich RMS norms, a hashed bigram embedding, windowed attention with sinks, latent attention in a window, the gated
+# delta rule: include/nvllm.h)
+
+
+def rms_residual_norm(h, y=None, post_w=None, pre_w=None, eps=1e-5, dtype=torch.bfloat16):
+    """h (f32 [n, hidden], in place) += rms(y) * post_w; returns rms(h) * pre_w in `dtype` (None without pre_w)."""
+    n, hidden = h.shape
+    out = torch.empty((n, hidden), dtype=dtype, device=h.device) if pre_w is not None else None
+    check(_ffi.lib().nvllm_rms_residual_norm(_p(out), _p(h), _p(y), _dt(y) if y is not None else F32, _p(post_w), _p(pre_w), n, hidden, eps,
+                                             BF16 if dtype == torch.bfloat16 else F32, _stream()))
+    return out
+
+
+def rms_norm_rows(x, weight, eps, dtype, out=None, row_map=None):
+    """rms(x[i]) * weight into out[row_map[i]] (a cache, rows < 0 skipped) or a new [n, cols] tensor; x f32 (row stride allowed)."""
+    n, cols = x.shape
+    if out is None:
+        out = torch.empty((n, cols), dtype=dtype, device=x.device)
+    check(_ffi.lib().nvllm_rms_norm_rows(_p(out), out.stride(0), _p(x), x.stride(0), _p(weight), _p(row_map), n, cols, eps, _dt(out), _stream()))
+    return out
+
+
+def embedding_bigram(table, bigram, ids, positions, tok_seq, cu_tokens, seq_slot, last_token, mul_prev, mul_cur, scale):
+    """table[ids] * scale + bigram[hash(previous, current)] as f32; last_token (int32 [slots]) is read and updated."""
+    n, hidden = ids.shape[0], table.shape[1]
+    h = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    check(_ffi.lib().nvllm_embedding_bigram(_p(h), _p(table), _p(bigram), _p(ids), _p(positions), _p(tok_seq), _p(cu_tokens), _p(seq_slot),
+                                            _p(last_token), n, hidden, table.shape[0], bigram.shape[0] - 1, mul_prev, mul_cur, float(scale),
+                                            _dt(table), _stream()))
+    return h
+
+
+def attn_rope_norm_store(proj, heads, kv_heads, dim, vdim, q_bias, k_bias, v_bias, positions, table, rot_dims, norm_eps, k_cache, v_cache,
+                         slots, dtype, v_from_k=False):
+    """proj: f32 [n, >= q + k (+ v) columns].  Returns q in `dtype`; k / v go to cache rows `slots`."""
+    n = proj.shape[0]
+    q = torch.empty((n, heads * dim), dtype=dtype, device=proj.device)
+    check(_ffi.lib().nvllm_attn_rope_norm_store(_p(q), q.stride(0), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(proj),
+                                                proj.stride(0), _p(q_bias), _p(k_bias), _p(v_bias), _p(positions), _p(table), rot_dims,
+                                                table.shape[0] if table is not None else 1, float(norm_eps), _p(slots), n, heads, kv_heads,
+                                                dim, vdim, int(v_from_k), _dt(q), _stream()))
+    return q
+
+
+def window_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, block_size, heads, kv_heads, dim, vdim, scale, window=0,
+                     sinks=None, gate_per_head=False, softcap=0.0, temp_coef=0.0, temp_every=1, cu_tokens=None):
+    n = q.shape[0]
+    out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
+    check(_ffi.lib().nvllm_window_attention(_p(out), out.stride(0), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                            int(gate_per_head), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(tok_seq),
+                                            _p(positions), _p(tables), tables.shape[1], block_size, n, heads, kv_heads, dim, vdim, scale,
+                                            softcap, temp_coef, temp_every, window, _p(sinks), _p(cu_tokens),
+                                            cu_tokens.shape[0] - 1 if cu_tokens is not None else 0, _dt(q), _stream()))
+    return out
+
+
+def latent_window_attention(q_abs, tok_seq, positions, tables, block_size, cache, heads, kv_rank, scale, dtype, window=0, sinks=None,
+                            gate=None):
+    """q_abs f32 [n, heads * kv_rank] (the key map folded into the query); cache [slots, row >= kv_rank] in `dtype`."""
+    n = q_abs.shape[0]
+    out = torch.empty((n, heads * kv_rank), dtype=dtype, device=q_abs.device)
+    check(_ffi.lib().nvllm_latent_window_attention(_p(out), out.stride(0), _p(q_abs), q_abs.stride(0), None, 0, _p(tok_seq), _p(positions),
+                                                   _p(tables), tables.shape[1], block_size, _p(cache), cache.stride(0), n, heads, 0, 0,
+                                                   kv_rank, scale, window, _p(sinks), _p(gate), gate.stride(0) if gate is not None else 0,
+                                                   _dt(out), _stream()))
+    return out
+
+
+def delta_prepare(q, k, beta, decay, a_log, dt_bias, heads, groups, dk, q_scale, unit_eps=1e-6):
+    """In place, f32: q / k [n, groups * dk] -> unit vectors (q scaled), beta [n, heads] -> sigmoid, decay [n, heads * dk] ->
+    exp(-exp(a_log) softplus(decay + dt_bias))."""
+    check(_ffi.lib().nvllm_delta_prepare(_p(q), q.stride(0), _p(k), k.stride(0), _p(beta), beta.stride(0), _p(decay), decay.stride(0), _p(a_log),
+                                         _p(dt_bias), q.shape[0], heads, groups, dk, float(q_scale), float(unit_eps), _stream()))
+
+
+def gated_delta_recurrence(q, k, v, decay, beta, state, seq_slot, cu_tokens, positions, heads, groups, dk, dv):
+    """S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T, y = S^T q over the sequences of a step; state [slots, heads, dk, dv]."""
+    n = v.shape[0]
+    y = torch.empty((n, heads * dv), dtype=torch.float32, device=v.device)
+    check(_ffi.lib().nvllm_gated_delta_recurrence(_p(y), y.stride(0), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(decay),
+                                                  decay.stride(0), _p(beta), beta.stride(0), _p(state), _p(seq_slot), _p(cu_tokens),
+                                                  _p(positions), seq_slot.shape[0], heads, groups, dk, dv, _stream()))
+    return y
+
+
+def gated_group_norm_act(y, gate, weight, parts, eps, gate_first, dtype, gate_act=0, w_shared=False):
+    """gated_group_norm with the gate's activation (0 SiLU, 1 sigmoid) and optionally one weight vector shared by the parts."""
+    n, cols = y.shape
+    out = torch.empty((n, cols), dtype=dtype, device=y.device)
+    check(_ffi.lib().nvllm_gated_group_norm_act(_p(out), out.stride(0), _p(y), y.stride(0), _p(gate), gate.stride(0), _p(weight), int(w_shared),
+                                                n, cols, parts, eps, int(gate_first), gate_act, _dt(out), _stream()))
+    return out
