@@ -53,11 +53,12 @@ def parse():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=None, help="override the workload model (qwen3-0.6b | qwen3-8b | qwen3-32b)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen", "talapel"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen", "talapel", "zudatar"],
                     help="kosazen: prefill / decode throughput and a per-kernel roofline table of the Kosazen architecture "
                          "(latent attention + mixture of experts) beside Qwen3 models of equal layer sizes, random weights; "
                          "talapel: the same for the Talapel architecture (capped attention beside a state-space mixer, retention, "
-                         "table-routed experts)")
+                         "table-routed experts); zudatar: the same for the Zudatar architecture (windowed attention, latent "
+                         "attention in a window, gated delta rule)")
     ap.add_argument("--seqs", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the in-run parity checks (profiling runs)")
@@ -746,6 +747,31 @@ def talapel_config(z):
             "layers": [par if i % 2 == 0 else ret for i in range(z["layers"])]}
 
 
+# Zudatar: a latent-attention layer, a gated-delta-rule layer without feed-forward, a windowed attention layer and a latent
+# layer that reads the first one's latents, at widths and head sizes of published hybrid models; windows half the prompt.
+# The Qwen3 arm: same width, depth, query / kv heads of 128, and an MLP as wide as the mean of what one Zudatar layer has.
+ZUDATAR_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, rot_dims=64, kv_rank=512, q_rank=768, d_heads=16, d_kv_heads=16,
+                  d_dim=128, d_vdim=128, taps=4, low_rank=128, dense_ff=8192, layers=4, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=512, rot_dims=64, kv_rank=512, q_rank=1536, d_heads=32, d_kv_heads=32,
+                  d_dim=128, d_vdim=128, taps=4, low_rank=256, dense_ff=12288, layers=4, vocab=32768),
+}
+
+
+def zudatar_config(z):
+    ff = {"kind": "dense", "ff": z["dense_ff"]}
+    lat = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": z["window"]}}
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": 1.0, "mask": {"size": z["window"]},
+           "rot": {"base": 10000.0, "dims": z["rot_dims"]}}
+    dlt = {"heads": z["d_heads"], "kv_heads": z["d_kv_heads"], "dim": z["d_dim"], "vdim": z["d_vdim"], "conv": z["taps"], "low_rank": z["low_rank"]}
+    kinds = [{"type": "latent_attention", "mixer": lat, "mlp": ff}, {"type": "channel_delta", "mixer": dlt, "mlp": None},
+             {"type": "attention", "mixer": att, "mlp": ff}, {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": ff}]
+    return {"architecture": "Zudatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 33, "mul_cur": 5}},
+            "layers": [kinds[i % 4] for i in range(z["layers"])]}
+
+
 def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
     """Algorithmic work of the named launches of ONE layer at n_tok tokens (context ctx per sequence): {name: (flop, bytes)}."""
     W, H, L = z["width"], z["heads"], ctx
@@ -782,6 +808,37 @@ def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
         # (nominal; the pool has no measured f32 figure).
         f32_tf = 148 * 128 * 2 * 1.965e9 / 1e12
         return {k: max(f / ((f32_tf if k.startswith("linear_recurrence") else tf) * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
+    if arch == "zudatar":
+        D, V, G, R, QR, w = z["dim"], z["vdim"], z["kv_heads"], z["kv_rank"], z["q_rank"], z["window"]
+        dH, dG, dD, dV, lr = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["low_rank"]
+        seqs = n_tok if decode else max(1, n_tok // L)
+        # (query, key) pairs per head inside the window
+        wpairs = n_tok * min(w, L) if decode else seqs * (min(w, L) * (min(w, L) + 1) / 2 + max(0, L - w) * w)
+        keys_read = n_tok * min(w, L) if decode else n_tok       # cache rows that must come from HBM
+        gemm = lambda n, k: (2 * n_tok * n * k, 2 * n * k + n_tok * (2 * k + 4 * n))
+        out["attention q k g projection"] = gemm(H * D + G * D + H, W)
+        out["window_attention"] = (4 * wpairs * H * D, keys_read * G * D * 2 * 2 + n_tok * H * D * 2 * 2)
+        # the two latent layers differ by the kv latent's columns: the mean of both
+        out["latent dq dkv g projection"] = gemm(QR + R // 2 + H, W)
+        out["query up-projection"] = gemm(H * D, QR)
+        out["q absorb (per-head GEMMs)"] = out["q absorb (per-head linear)"] = (2 * n_tok * H * D * R, 2 * H * D * R + n_tok * H * (2 * D + 4 * R))
+        out["latent_window_attention"] = (4 * wpairs * H * R, keys_read * R * 2 + n_tok * H * R * 6)
+        out["value up-projection (per-head GEMMs)"] = out["value up-projection (per-head linear)"] = (2 * n_tok * H * V * R, 2 * H * V * R + n_tok * H * 2 * (R + V))
+        out["mixer output projection"] = gemm(W, H * V)
+        ch = 2 * dG * dD + dH * dV
+        out["delta q k v b projection"] = gemm(ch + dH, W)
+        out["delta decay / gate first step"] = gemm(2 * lr, W)
+        out["delta decay second step"] = gemm(dH * dD, lr)
+        out["delta gate second step"] = gemm(dH * dV, lr)
+        out["causal_conv"] = (2 * n_tok * ch * z["taps"], n_tok * ch * 8)
+        # 8 flop per state element and token (decay, two read-outs, the write); the state is read and written once per portion
+        out["gated_delta_recurrence"] = (8 * n_tok * dH * dD * dV, n_tok * (2 * dG * dD + dH * dD + 2 * dH * dV) * 4 + seqs * dH * dD * dV * 8)
+        out["gate_up projection"] = out["gate_up projection + SiLU gate"] = gemm(2 * z["dense_ff"], W)
+        out["down projection"] = gemm(W, z["dense_ff"])
+        out["rms_residual_norm"] = (0, n_tok * W * (4 + 4 + 4 + 2))
+        # the recurrence runs in f32 by definition of the design: its compute bound is the f32 FMA rate of the CUDA cores
+        f32_tf = 148 * 128 * 2 * 1.965e9 / 1e12
+        return {k: max(f / ((f32_tf if k == "gated_delta_recurrence" else tf) * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
     if arch == "kosazen":
         r, rd, d, vd, E, ff, top, sff = z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["experts"], z["ff"], z["top"], z["shared_ff"]
         out["latent_attention"] = (2 * pairs * H * (2 * r + rd), (n_tok // max(1, L) if not decode else n_tok) * L * (r + rd) * 2 + n_tok * H * (2 * r + rd) * 4)
@@ -812,7 +869,7 @@ def run_arch_compare(args, new_arch="kosazen"):
     rng = __import__("numpy").random.default_rng(0)
     result = {"workload": f"{new_arch}-vs-qwen3", "data": "synthetic", "dtype": "bf16", "prefill": f"{n_prompts} x {plen} tokens per step",
               "decode": f"{dec_b} sequences at context {plen}+", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf}, "sizes": {}}
-    sizes = ARCH_SIZES if new_arch == "kosazen" else TALAPEL_SIZES
+    sizes = {"kosazen": ARCH_SIZES, "talapel": TALAPEL_SIZES, "zudatar": ZUDATAR_SIZES}[new_arch]
     only = os.environ.get("BENCH_ARCH_SIZES")          # e.g. "w2048": a subset of the sizes
     for name, z in sizes.items():
         if only and name not in only.split(","):
@@ -820,6 +877,9 @@ def run_arch_compare(args, new_arch="kosazen"):
         if new_arch == "talapel":   # the Qwen3 arm's fields: an MLP as wide as the mean of what one token uses per layer
             z = dict(z, shared_ff=0)
             mlp_q = (z["dense_ff"] + z["top"] * z["ff"]) // 2 // 64 * 64
+        elif new_arch == "zudatar":   # three of four layers have a feed-forward
+            z = dict(z, shared_ff=0, top=0, ff=0)
+            mlp_q = z["dense_ff"] * 3 // 4 // 64 * 64
         else:
             mlp_q = z["top"] * z["ff"] + z["shared_ff"]
         result["sizes"][name] = {}
@@ -832,6 +892,8 @@ def run_arch_compare(args, new_arch="kosazen"):
                 cfg = E.Config(model_config=kosazen_config(z), **common)
             elif arch == "talapel":
                 cfg = E.Config(model_config=talapel_config(z), **common)
+            elif arch == "zudatar":
+                cfg = E.Config(model_config=zudatar_config(z), **common)
             else:
                 cfg = E.Config("qwen3-0.6b", vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
                                intermediate_size=mlp_q, num_attention_heads=z["heads"],
@@ -936,6 +998,10 @@ def main():
     torch.cuda.set_device(local)
     lib = E.lib()
     assert lib.nvllm_device_ok() == 1, "no sm_100 device: the product path has no fallback"
+    if args.workload == "zudatar":
+        assert world == 1, "--workload zudatar is a one-GPU comparison"
+        print(json.dumps(run_arch_compare(args, "zudatar")), flush=True)
+        return 0
     if args.workload == "talapel":
         assert world == 1, "--workload talapel is a one-GPU comparison"
         print(json.dumps(run_arch_compare(args, "talapel")), flush=True)
