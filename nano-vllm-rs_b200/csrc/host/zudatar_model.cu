@@ -103,7 +103,8 @@ class Zudatar : public ModelImpl {
   float* final_norm_ = nullptr;
   std::map<std::pair<double, int>, float*> rope_tables_;
   // activations
-  float *h_ = nullptr, *proj_ = nullptr, *sub_out_ = nullptr, *q_abs_ = nullptr, *conv_out_ = nullptr, *decay_ = nullptr, *gate_ = nullptr, *y_ = nullptr;
+  float *h_ = nullptr, *proj_ = nullptr, *q_abs_ = nullptr, *conv_out_ = nullptr, *decay_ = nullptr, *gate_ = nullptr, *y_ = nullptr;
+  void *sub_out_ = nullptr;   // a sublayer's output in the operand type; its norm and the residual sum are f32
   void *normed_ = nullptr, *q_ = nullptr, *cq_ = nullptr, *o_lat_ = nullptr, *mix_in_ = nullptr, *lr_out_ = nullptr, *gu_buf_ = nullptr, *act_ = nullptr,
        *head_in_ = nullptr;
   int head_rows_ = 0;
@@ -278,7 +279,7 @@ class Zudatar : public ModelImpl {
         m_ff = std::max<size_t>(m_ff, L.ff);
       }
     }
-    RUN(dalloc(&h_, T * W)); RUN(oalloc(&normed_, T * W)); RUN(dalloc(&proj_, T * m_proj)); RUN(dalloc(&sub_out_, T * W));
+    RUN(dalloc(&h_, T * W)); RUN(oalloc(&normed_, T * W)); RUN(dalloc(&proj_, T * m_proj)); RUN(oalloc(&sub_out_, T * W));
     RUN(oalloc(&q_, T * m_q)); RUN(oalloc(&cq_, T * m_cq)); RUN(dalloc(&q_abs_, T * m_lat)); RUN(oalloc(&o_lat_, T * m_lat));
     RUN(oalloc(&mix_in_, T * m_mix)); RUN(dalloc(&conv_out_, T * m_ch)); RUN(dalloc(&decay_, T * m_hd)); RUN(dalloc(&gate_, T * m_hv));
     RUN(dalloc(&y_, T * m_hv));
@@ -505,9 +506,9 @@ class Zudatar : public ModelImpl {
       return rc;
     };
     // h += rms(y) * post;  normed = rms(h) * pre
-    auto norm = [&](const float* y, const float* post, const float* pre) {
+    auto norm = [&](const void* y, const float* post, const float* pre) {
       ++launches;
-      const int rc = nvllm_rms_residual_norm(normed_, h_, y, NVLLM_F32, post, pre, N, W, eps_, dt_, st);
+      const int rc = nvllm_rms_residual_norm(normed_, h_, y, dt_, post, pre, N, W, eps_, dt_, st);
       mk("rms_residual_norm");
       return rc;
     };
@@ -585,7 +586,7 @@ class Zudatar : public ModelImpl {
                                          v.seq_slots, v.cu_tokens, v.positions, S, L.H, L.G, L.D, L.V, st)); ++launches; mk("gated_delta_recurrence");
         RUN(nvllm_gated_group_norm_act(mix_in_, HV, y_, HV, gate_, HV, L.o_norm, 1, N, HV, L.H, eps_, 0, 1, dt_, st)); ++launches; mk("gated_group_norm");
       }
-      RUN(lin(sub_out_, mix_in_, L.o, W, HV, HV, W, NVLLM_F32, "mixer output projection"));
+      RUN(lin(sub_out_, mix_in_, L.o, W, HV, HV, W, dt_, "mixer output projection"));
       if (L.has_mlp) {
         RUN(norm(sub_out_, L.norm1b, L.norm2));
         if (dt_ == NVLLM_BF16 && L.ff % 128 == 0 && W % 64 == 0) {  // SiLU gate in the GEMM's epilogue: [N, 2 ff] never reaches HBM
@@ -594,7 +595,7 @@ class Zudatar : public ModelImpl {
           RUN(lin(gu_buf_, normed_, L.gu, 2 * L.ff, W, W, 2 * L.ff, dt_, "gate_up projection"));
           RUN(nvllm_ff_activation(act_, gu_buf_, N, L.ff, 0, dt_, st)); ++launches; mk("ff_activation (silu gate)");
         }
-        RUN(lin(sub_out_, act_, L.down, W, L.ff, L.ff, W, NVLLM_F32, "down projection"));
+        RUN(lin(sub_out_, act_, L.down, W, L.ff, L.ff, W, dt_, "down projection"));
         RUN(norm(sub_out_, L.norm2b, next));
       } else {
         RUN(norm(sub_out_, L.norm1b, next));

@@ -584,6 +584,49 @@ __global__ void __launch_bounds__(128) gated_group_norm_vec_kernel(TO* __restric
   }
 }
 
+// Parts of up to 512 values: one WARP per (token, part), four parts per CTA, the part's values in registers.
+template <typename TO>
+__global__ void __launch_bounds__(128) gated_group_norm_warp_kernel(TO* __restrict__ out, int64_t ldo, const float* __restrict__ y, int64_t ldy,
+                                                                    const float* __restrict__ z, int64_t ldz, const float* __restrict__ w, int gs,
+                                                                    int parts, int64_t items, float eps, int gate_first, int act, int wst) {
+  const int lane = threadIdx.x & 31, nv = gs / 4;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int64_t t = item / parts;
+  const int g = static_cast<int>(item - t * parts);
+  const float4* yr = reinterpret_cast<const float4*>(y + t * ldy + static_cast<int64_t>(g) * gs);
+  const float4* zr = reinterpret_cast<const float4*>(z + t * ldz + static_cast<int64_t>(g) * gs);
+  float4 v[4], sg[4];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < nv) {
+      v[k] = yr[c];
+      const float4 zz = zr[c];
+      sg[k] = make_float4(gate_f(zz.x, act), gate_f(zz.y, act), gate_f(zz.z, act), gate_f(zz.w, act));
+      if (gate_first) { v[k].x *= sg[k].x; v[k].y *= sg[k].y; v[k].z *= sg[k].z; v[k].w *= sg[k].w; }
+      sq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  const float r = rsqrtf(warp_sum(sq) / gs + eps);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < nv) {
+      float4 o = make_float4(v[k].x * r, v[k].y * r, v[k].z * r, v[k].w * r);
+      if (!gate_first) { o.x *= sg[k].x; o.y *= sg[k].y; o.z *= sg[k].z; o.w *= sg[k].w; }
+      if (w) {
+        const float4 ww = reinterpret_cast<const float4*>(w + static_cast<int64_t>(g) * wst)[c];
+        o.x *= ww.x; o.y *= ww.y; o.z *= ww.z; o.w *= ww.w;
+      }
+      const int64_t at = t * ldo + static_cast<int64_t>(g) * gs + 4 * c;
+      if (sizeof(TO) == 2) *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + at) = make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
+      else *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at) = o;
+    }
+  }
+}
+
 inline unsigned grid_for(int64_t total) {
   int64_t b = (total + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -750,6 +793,17 @@ extern "C" int nvllm_gated_group_norm_act(void* out, int64_t ldo, const float* y
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(static_cast<int64_t>(n) * parts);
   const int gs = cols / parts, wst = w_shared ? 0 : gs;
+  const bool vec_ok = gs % 4 == 0 && ldo % 4 == 0 && ldy % 4 == 0 && ldg % 4 == 0 && aligned16(out) && aligned16(y) && aligned16(gate) && aligned16(w);
+  if (vec_ok && gs <= 512) {
+    const int64_t items = static_cast<int64_t>(n) * parts;
+    const unsigned wgrid = static_cast<unsigned>((items + 3) / 4);
+    if (out_dtype == NVLLM_BF16)
+      gated_group_norm_warp_kernel<bf16><<<wgrid, 128, 0, st>>>(static_cast<bf16*>(out), ldo, y, ldy, gate, ldg, w, gs, parts, items, eps, gate_first, gate_act, wst);
+    else
+      gated_group_norm_warp_kernel<float><<<wgrid, 128, 0, st>>>(static_cast<float*>(out), ldo, y, ldy, gate, ldg, w, gs, parts, items, eps, gate_first, gate_act, wst);
+    NVLLM_LAUNCH_CHECK("gated_group_norm_warp_kernel");
+    return 0;
+  }
   if (gs % 4 == 0 && gs <= 2048 && ldo % 4 == 0 && ldy % 4 == 0 && ldg % 4 == 0 && aligned16(out) && aligned16(y) && aligned16(gate) && aligned16(w)) {
     if (out_dtype == NVLLM_BF16)
       gated_group_norm_vec_kernel<bf16><<<grid, 128, 0, st>>>(static_cast<bf16*>(out), ldo, y, ldy, gate, ldg, w, gs, parts, eps, gate_first, gate_act, wst);

@@ -71,6 +71,66 @@ __global__ void __launch_bounds__(256) rms_residual_norm_kernel(TO* __restrict__
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) st_as(out, base + c, row[c] * r * pre_w[c]);
 }
 
+// The same for rows of up to 8192 values in 16-byte vectors: the row stays in registers (one global pass), y and out in f32 or bf16.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256) rms_residual_norm_vec_kernel(TO* __restrict__ out, float* __restrict__ h, const TY* __restrict__ y,
+                                                                    const float* __restrict__ post_w, const float* __restrict__ pre_w, int hidden,
+                                                                    float eps) {
+  __shared__ float red[8];
+  const int nv = hidden / 4;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
+  float4 v[8];
+  float sq = 0.f;
+  if (y != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = threadIdx.x + 256 * k;
+      if (c < nv) {
+        if (sizeof(TY) == 2) {
+          const uint2 u = reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(y) + base)[c];
+          v[k] = make_float4(bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y));
+        } else {
+          v[k] = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + base)[c];
+        }
+        sq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+      }
+    }
+    const float r = 1.0f / sqrtf(block_sum(sq, red) / hidden + eps);
+    sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = threadIdx.x + 256 * k;
+      if (c < nv) {
+        const float4 hv = reinterpret_cast<const float4*>(h + base)[c], w = reinterpret_cast<const float4*>(post_w)[c];
+        v[k] = make_float4(hv.x + v[k].x * r * w.x, hv.y + v[k].y * r * w.y, hv.z + v[k].z * r * w.z, hv.w + v[k].w * r * w.w);
+        reinterpret_cast<float4*>(h + base)[c] = v[k];
+        sq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = threadIdx.x + 256 * k;
+      if (c < nv) {
+        v[k] = reinterpret_cast<const float4*>(h + base)[c];
+        sq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+      }
+    }
+  }
+  if (out == nullptr) return;
+  const float r = 1.0f / sqrtf(block_sum(sq, red) / hidden + eps);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = threadIdx.x + 256 * k;
+    if (c < nv) {
+      const float4 w = reinterpret_cast<const float4*>(pre_w)[c];
+      const float4 o = make_float4(v[k].x * r * w.x, v[k].y * r * w.y, v[k].z * r * w.z, v[k].w * r * w.w);
+      if (sizeof(TO) == 2) reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + base)[c] = make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
+      else reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + base)[c] = o;
+    }
+  }
+}
+
 // One warp per row.
 template <typename TO>
 __global__ void __launch_bounds__(128) rms_norm_rows_kernel(TO* __restrict__ out, int64_t ldo, const float* __restrict__ x, int64_t ldx,
@@ -141,6 +201,15 @@ extern "C" int nvllm_rms_residual_norm(void* out, float* h, const void* y, int32
   if (n == 0) return 0;
   NVLLM_CHECK_ARG(h && (out || y) && (!y || post_w) && (!out || pre_w), NVLLM_ERR_ARG, "rms_residual_norm: NULL");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (hidden % 4 == 0 && hidden <= 8192 && aligned16(h) && aligned16(y) && aligned16(out) && aligned16(post_w) && aligned16(pre_w)) {
+    const bool yb = y_dtype == NVLLM_BF16, ob = out_dtype == NVLLM_BF16;
+    if (yb && ob) rms_residual_norm_vec_kernel<bf16, bf16><<<n, 256, 0, st>>>(static_cast<bf16*>(out), h, static_cast<const bf16*>(y), post_w, pre_w, hidden, eps);
+    else if (yb) rms_residual_norm_vec_kernel<bf16, float><<<n, 256, 0, st>>>(static_cast<float*>(out), h, static_cast<const bf16*>(y), post_w, pre_w, hidden, eps);
+    else if (ob) rms_residual_norm_vec_kernel<float, bf16><<<n, 256, 0, st>>>(static_cast<bf16*>(out), h, static_cast<const float*>(y), post_w, pre_w, hidden, eps);
+    else rms_residual_norm_vec_kernel<float, float><<<n, 256, 0, st>>>(static_cast<float*>(out), h, static_cast<const float*>(y), post_w, pre_w, hidden, eps);
+    NVLLM_LAUNCH_CHECK("rms_residual_norm_vec_kernel");
+    return 0;
+  }
   const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
   if (out_dtype == NVLLM_BF16) {
     NVLLM_SMEM_ATTR_ONCE(rms_residual_norm_kernel<bf16>, 192 * 1024);
