@@ -2,7 +2,7 @@
 // grouped / gathered variants a mixture-of-experts layer needs (nvllm_linear_grouped) and the gated pair with its
 // activation in the epilogue (GLU).  Dense bf16 problems whose shapes meet the tensor-core kernel's rules (k % 64, n % 8,
 // 16-byte rows) are forwarded to nvllm_gemm_bf16 (tcgen05); everything else — odd sizes, per-head batches, expert groups,
-// true 32-bit models — runs on the CUDA-core tile kernel below: 32 x 64 output tile, 32-wide k steps staged in shared
+// true 32-bit models — runs on the CUDA-core tile kernel below (bf16 problems with 16-byte rows: on an mma.sync tile kernel): 32 x 64 output tile, 32-wide k steps staged in shared
 // memory as f32, f32 accumulation in ascending k order, so a row's result never depends on which other rows are in the
 // batch.
 #include "common.cuh"
@@ -173,6 +173,92 @@ __global__ void ff_activation_kernel(T* __restrict__ out, const T* __restrict__ 
   }
 }
 
+// ---- batched products with few rows on tensor cores (bf16) ------------------------------------------------------------
+// Per-head projections while decoding (a handful of tokens times `heads` small weight blocks) and products whose reduction
+// size the tcgen05 kernel does not take (k % 64 != 0).  CTA = 64 rows x BN columns of ONE batch item, 4 warps of 16 rows;
+// 64-wide k steps of x and w staged with cp.async (16-byte chunks, zero fill past k), double-buffered; mma.sync m16n8k16
+// with f32 accumulation in ascending k, so a row never depends on which other rows are in the batch.
+constexpr int MK = 64, MS = MK + 8;   // k step and the shared-memory row stride (conflict-free ldmatrix)
+
+template <int BNT, typename TO>
+__global__ void __launch_bounds__(128) linear_mma_kernel(const LinArgs a) {
+  __shared__ __align__(16) bf16 xs[2][64][MS];
+  __shared__ __align__(16) bf16 ws[2][BNT][MS];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq4 = lane & 3;
+  const int b = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * BNT;
+  const bf16* x = static_cast<const bf16*>(a.x) + b * a.bsx;
+  const bf16* w = static_cast<const bf16*>(a.w) + b * a.bsw;
+  TO* y = static_cast<TO*>(a.y) + b * a.bsy;
+  auto load = [&](int k0, int buf) {
+    for (int e = tid; e < (64 + BNT) * (MK / 8); e += 128) {
+      const int r = e / (MK / 8), c = (e % (MK / 8)) * 8, k = k0 + c;
+      const bool is_x = r < 64;
+      const int row = is_x ? m0 + r : n0 + r - 64;
+      const bool ok = k < a.K && row < (is_x ? a.M : a.N);
+      const bf16* src = is_x ? x + static_cast<int64_t>(row) * a.ldx + k : w + static_cast<int64_t>(row) * a.ldw + k;
+      cp_async_16(smem_u32(is_x ? &xs[buf][r][c] : &ws[buf][r - 64][c]), ok ? src : static_cast<const bf16*>(a.x), ok ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+  float acc[BNT / 8][4];
+#pragma unroll
+  for (int i = 0; i < BNT / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int nk = (a.K + MK - 1) / MK;
+  load(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < nk) { load((kt + 1) * MK, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const uint32_t xa = smem_u32(&xs[buf][warp * 16 + (lane & 15)][(lane >> 4) * 8]);
+    const uint32_t wa = smem_u32(&ws[buf][(lane & 7) + (lane >> 4) * 8][((lane >> 3) & 1) * 8]);
+#pragma unroll
+    for (int kk = 0; kk < MK / 16; ++kk) {
+      uint32_t af[4];
+      ldmatrix_x4(af, xa + kk * 32);
+#pragma unroll
+      for (int np = 0; np < BNT / 16; ++np) {
+        uint32_t bw[4];
+        ldmatrix_x4(bw, wa + np * 16 * MS * 2 + kk * 32);
+        mma_bf16_16816(acc[2 * np], af, bw[0], bw[1]);
+        mma_bf16_16816(acc[2 * np + 1], af, bw[2], bw[3]);
+      }
+    }
+    __syncthreads();   // the copy issued in the next iteration overwrites this buffer's partner
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + warp * 16 + gq + 8 * i;
+    if (m >= a.M) continue;
+#pragma unroll
+    for (int nt = 0; nt < BNT / 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int n = n0 + nt * 8 + 2 * tq4 + c;
+        if (n < a.N) stf(y + static_cast<int64_t>(m) * a.ldy + n, acc[nt][2 * i + c]);
+      }
+  }
+}
+
+inline bool mma_applies(const LinArgs& a) {
+  return a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 && a.bsx % 8 == 0 && a.bsw % 8 == 0 && aligned16(a.x) && aligned16(a.w);
+}
+
+int launch_mma(const LinArgs& a, int batch, int out_dtype, cudaStream_t st) {
+  // narrow tiles while the grid would leave most SMs idle
+  const int64_t ctas64 = static_cast<int64_t>((a.N + 63) / 64) * ((a.M + 63) / 64) * batch;
+  if (ctas64 >= sm_count() || a.N <= 32) {
+    dim3 grid((a.N + 63) / 64, (a.M + 63) / 64, batch);
+    if (out_dtype == NVLLM_BF16) linear_mma_kernel<64, bf16><<<grid, 128, 0, st>>>(a);
+    else linear_mma_kernel<64, float><<<grid, 128, 0, st>>>(a);
+  } else {
+    dim3 grid((a.N + 31) / 32, (a.M + 63) / 64, batch);
+    if (out_dtype == NVLLM_BF16) linear_mma_kernel<32, bf16><<<grid, 128, 0, st>>>(a);
+    else linear_mma_kernel<32, float><<<grid, 128, 0, st>>>(a);
+  }
+  NVLLM_LAUNCH_CHECK("linear_mma_kernel");
+  return 0;
+}
+
 template <bool GLU>
 int launch_tile(const LinArgs& a, int m_tiles, int batch, int dtype, int out_dtype, cudaStream_t st) {
   dim3 grid((a.N + BN - 1) / BN, m_tiles, batch);
@@ -203,6 +289,8 @@ extern "C" int nvllm_linear(void* y, const void* x, const void* w, int32_t m, in
       aligned16(y) && aligned16(x) && aligned16(w))
     return nvllm_gemm_bf16(y, x, w, m, n, k, ldx, ldw, ldy, out_dtype, nullptr, 0, stream);
   LinArgs a{y, x, w, m, n, k, ldx, ldw, ldy, bsx, bsw, bsy, nullptr, nullptr, 0, 0.f, 0};
+  // other bf16 problems with 16-byte rows (per-head batches, reduction sizes that are not multiples of 64): mma.sync tiles
+  if (dtype == NVLLM_BF16 && knobs().linear_mma && mma_applies(a)) return launch_mma(a, batch, out_dtype, static_cast<cudaStream_t>(stream));
   return launch_tile<false>(a, (m + BM - 1) / BM, batch, dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }
 

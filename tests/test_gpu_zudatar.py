@@ -432,6 +432,33 @@ def test_gated_group_norm_sigmoid_gate_shared_weight(cuda, dtype, cols, parts):
     np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k,heads", [(1, 40, 24, 1), (5, 64, 128, 6), (64, 128, 512, 4), (70, 24, 72, 3), (130, 513, 8, 2), (300, 16, 200, 5)])
+def test_batched_small_products_on_tensor_cores(cuda, monkeypatch, m, n, k, heads, out_dtype):
+    """Per-head products y_h = x_h . w_h^T out of packed activations (few rows, reduction sizes that are not multiples of
+    64): the mma.sync tile kernel against float64, and against the CUDA-core tile kernel it stands in for."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(m + n + k)
+    x = Z.bf16_round(rng.standard_normal((m, heads * k + 8)))
+    w = Z.bf16_round(rng.standard_normal((heads * n, k)) / np.sqrt(k))
+    xd, wd = dev_t(x, cuda, torch.bfloat16), dev_t(w, cuda, torch.bfloat16)
+    run = lambda: ops.linear(xd, wd, out_dtype, batch=heads, bsx=k, bsw=n * k, bsy=n, n=n, k=k,
+                             out=torch.zeros((m, heads * n), dtype=out_dtype, device=cuda)).float().cpu().numpy()
+    got = run()
+    ref = np.concatenate([x[:, h * k:(h + 1) * k] @ w[h * n:(h + 1) * n].T for h in range(heads)], axis=1)
+    tol = 1e-2 if out_dtype == torch.bfloat16 else 2e-5
+    np.testing.assert_allclose(got, ref, rtol=tol, atol=tol)
+    monkeypatch.setenv("NVLLM_LINEAR_MMA", "0")
+    np.testing.assert_allclose(run(), got, rtol=tol, atol=tol)
+    # a row's result does not depend on the rows beside it
+    one = ops.linear(xd[m - 1:], wd, out_dtype, batch=heads, bsx=k, bsw=n * k, bsy=n, n=n, k=k,
+                     out=torch.zeros((1, heads * n), dtype=out_dtype, device=cuda)).float().cpu().numpy()
+    monkeypatch.delenv("NVLLM_LINEAR_MMA")
+    one2 = ops.linear(xd[m - 1:], wd, out_dtype, batch=heads, bsx=k, bsw=n * k, bsy=n, n=n, k=k,
+                      out=torch.zeros((1, heads * n), dtype=out_dtype, device=cuda)).float().cpu().numpy()
+    assert np.array_equal(one2, got[m - 1:]) and np.allclose(one, got[m - 1:], rtol=tol, atol=tol)
+
+
 # ------------------------------------------------------------------------------------------------ the engine
 
 
