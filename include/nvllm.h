@@ -517,7 +517,9 @@ int nvllm_attn_rope_norm_store(void* q, int64_t ldq, void* k_cache, void* v_cach
                                int32_t vdim, int32_t v_from_k, int32_t dtype, void* stream);
 /* nvllm_capped_attention with three more options: window > 0: position p sees only the keys p - window + 1 .. p;
  * sinks (f32 [heads], nullable): exp(sinks[h]) joins the softmax denominator (unscaled, no value);
- * gate_per_head != 0: gate is [n, heads] (ldg apart) and head h's output is multiplied by sigmoid(gate[t, h]). */
+ * gate_per_head != 0: gate is [n, heads] (ldg apart) and head h's output is multiplied by sigmoid(gate[t, h]).
+ * block_tables == NULL (cu_tokens given): the keys are not paged — every sequence of the step starts at position 0 and key
+ * j of sequence s is row cu_tokens[s] + j of k_cache / v_cache (whole prompts whose keys were just computed). */
 int nvllm_window_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
                            int32_t gate_per_head, const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
                            const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables, int32_t table_cap,

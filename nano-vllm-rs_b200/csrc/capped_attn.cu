@@ -115,6 +115,7 @@ struct AttnArgs {
   int table_cap, block_size, n, heads, kv_heads, dim, vdim;
   float scale, softcap, temp_coef; int temp_every;
   int window; const float* sinks; int gate_per_head;
+  const int32_t* dense_cu;   // non-null (and tables null): keys are not paged, key j of sequence s is row dense_cu[s] + j
 };
 
 constexpr int kMaxVPerLane = 16;  // vdim <= 512
@@ -136,7 +137,8 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
   const T* q = static_cast<const T*>(a.q) + t * a.ldq + static_cast<int64_t>(h) * a.dim;
   for (int c = lane; c < a.dim; c += 32) qw[c] = ldv(q + c) * qscale;
   __syncwarp();
-  const int32_t* table = a.tables + static_cast<int64_t>(a.tok_seq[t]) * a.table_cap;
+  const int32_t* table = a.tables ? a.tables + static_cast<int64_t>(a.tok_seq[t]) * a.table_cap : nullptr;
+  const int64_t dense0 = a.dense_cu ? a.dense_cu[a.tok_seq[t]] : 0;
   const T* kc = static_cast<const T*>(a.kc) + static_cast<int64_t>(g) * a.dim;
   const T* vc = static_cast<const T*>(a.vc) + static_cast<int64_t>(g) * a.vdim;
   float m = -INFINITY, l = 0.f, acc[kMaxVPerLane];
@@ -149,9 +151,9 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
     float s = -INFINITY;
     int64_t slot = -1;
     if (j < nkeys && j >= first) {
-      const int32_t blk = table[j / a.block_size];
+      const int32_t blk = table ? table[j / a.block_size] : 0;
       if (blk >= 0) {
-        slot = static_cast<int64_t>(blk) * a.block_size + j % a.block_size;
+        slot = table ? static_cast<int64_t>(blk) * a.block_size + j % a.block_size : dense0 + j;
         const T* kr = kc + slot * a.k_row;
         float d = 0.f;
         for (int c = 0; c < a.dim; ++c) d = fmaf(qw[c], ldv(kr + c), d);
@@ -313,7 +315,8 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   }
   if (seq < 0) return;
   const int nkeys = static_cast<int>(a.positions[tok0 + ntok - 1]) + 1;   // tokens of a sequence are in order of position
-  const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
+  const int32_t* table = a.tables ? a.tables + static_cast<int64_t>(seq) * a.table_cap : nullptr;
+  const int64_t dense0 = cu_tokens[seq];
   const bf16* qg = static_cast<const bf16*>(a.q);
   const bf16* kc = static_cast<const bf16*>(a.kc) + static_cast<int64_t>(g) * a.dim;
   const bf16* vc = static_cast<const bf16*>(a.vc) + static_cast<int64_t>(g) * a.vdim;
@@ -334,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   auto lookup = [&](int kt) -> int64_t {          // threads 0..63: key kt * 64 + tid
     const int j = kt * kKeys + tid;
     if (j >= nkeys) return -1;
+    if (table == nullptr) return dense0 + j;
     const int32_t blk = table[j / a.block_size];
     return blk >= 0 ? static_cast<int64_t>(blk) * a.block_size + j % a.block_size : -1;
   };
@@ -563,9 +567,9 @@ extern "C" int nvllm_window_attention(void* out, int64_t ldo, const void* q, int
                   "attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 512)", n, heads, kv_heads, dim, vdim);
   NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "attention: dtype %d", dtype);
   if (n == 0) return 0;
-  NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && block_tables, NVLLM_ERR_ARG, "attention: NULL");
+  NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && (block_tables || cu_tokens), NVLLM_ERR_ARG, "attention: NULL");
   AttnArgs a{out, ldo, q, ldq, gate, ldg, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables, table_cap, block_size,
-             n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window > 0 ? window : 0, sinks, gate_per_head};
+             n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window > 0 ? window : 0, sinks, gate_per_head, block_tables ? nullptr : cu_tokens};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 with 16-byte rows and a token range per sequence: tensor cores; everything else (f32, odd sizes): one warp per row
   const int group = heads / kv_heads;

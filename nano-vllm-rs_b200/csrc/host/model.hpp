@@ -40,6 +40,7 @@ struct StepView {
   float* logits = nullptr;            // [n_logit_rows, vocab]
   float* layer_tap = nullptr;         // host memory, or null: the f32 residual stream after every layer run, [runs, n_tokens, width]
   bool capturing = false;
+  bool whole_prompts = false;         // every sequence of the step starts at position 0 (known on the host): its keys are the step's own rows
   // per-launch profile of eager steps (nvllm_runner_profile): called after every launch with the kernel's name
   void (*mark)(void* ctx, const char* name) = nullptr;
   void* mark_ctx = nullptr;

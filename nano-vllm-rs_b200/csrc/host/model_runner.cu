@@ -129,6 +129,7 @@ struct nvllm_runner {
   std::unique_ptr<ModelImpl> model;
   int model_dtype = NVLLM_BF16;
   int32_t *d_tok_seq = nullptr, *d_logit_rows = nullptr;  // into d_meta: sequence of every token, tokens that feed the head
+  bool step_whole_prompts = false;   // the uploaded step holds only portions that start at position 0
   int32_t *d_cu_tokens = nullptr, *d_seq_slots = nullptr;  // into d_meta: token range and recurrent-state slot of every sequence
   int n_logit_rows = 0, logit_cap = 0;
   bool explicit_rows = false;
@@ -255,6 +256,7 @@ int nvllm_runner::forward_model(int N, int S) {
   v.ids = d_ids; v.positions = d_pos; v.slots = d_slots; v.tok_seq = d_tok_seq; v.tables = d_tables; v.table_cap = table_cap;
   v.logit_rows = d_logit_rows; v.n_logit_rows = n_logit_rows; v.logits = logits;
   v.cu_tokens = d_cu_tokens; v.seq_slots = d_seq_slots;
+  v.whole_prompts = step_whole_prompts;
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   v.capturing = cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
   v.layer_tap = layer_tap;
@@ -539,6 +541,9 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
     }
     d_cu_tokens = d_cu_q;
     d_seq_slots = nullptr;
+    step_whole_prompts = S > 0;
+    for (size_t i = 0; i < S; ++i)
+      if (b.cu_seqlens_q[i + 1] > b.cu_seqlens_q[i] && b.positions[b.cu_seqlens_q[i]] != 0) step_whole_prompts = false;
     if (model && model->recurrent_state()) {
       NVLLM_CHECK_ARG(b.state_slots != nullptr, NVLLM_ERR_ARG, "execute: this model needs a state slot per sequence (nvllm_batch.state_slots)");
       for (size_t i = 0; i < S; ++i)
@@ -581,6 +586,7 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
       explicit_rows = false;
     }
     d_cu_tokens = d_seq_slots = nullptr;
+    step_whole_prompts = false;
     if (model) {  // token range of sequence i = [i, i + 1); padding sequences have no state slot
       int32_t* cu = reinterpret_cast<int32_t*>(h_meta + used);
       d_cu_tokens = reinterpret_cast<int32_t*>(d_meta + used);

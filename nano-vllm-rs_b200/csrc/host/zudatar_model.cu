@@ -70,6 +70,7 @@ struct Layer {
   float *qb = nullptr, *kb = nullptr;            // attention biases
   float *dq_norm = nullptr, *dkv_norm = nullptr, *sink = nullptr;
   void *uq = nullptr, *ukT = nullptr, *uv = nullptr;   // ukT: per head [kv_rank, dim]
+  void* ukv = nullptr;                                 // [uk | uv] as stored, [H * (dim + vdim), kv_rank]: keys and values of whole prompts
   float *conv_w = nullptr, *a_log = nullptr, *dt_bias = nullptr, *o_norm = nullptr;
   void *a1 = nullptr, *g1 = nullptr, *lr = nullptr, *a2 = nullptr, *g2 = nullptr;   // lr: [a1 | g1] packed once both are known
   void *gu = nullptr, *down = nullptr;
@@ -104,6 +105,7 @@ class Zudatar : public ModelImpl {
   std::map<std::pair<double, int>, float*> rope_tables_;
   // activations
   float *h_ = nullptr, *proj_ = nullptr, *q_abs_ = nullptr, *conv_out_ = nullptr, *decay_ = nullptr, *gate_ = nullptr, *y_ = nullptr;
+  void *kv_ = nullptr, *c_dense_ = nullptr;   // whole prompts of a latent layer: the step's latents and their keys / values per head
   void *sub_out_ = nullptr;   // a sublayer's output in the operand type; its norm and the residual sum are f32
   void *normed_ = nullptr, *q_ = nullptr, *cq_ = nullptr, *o_lat_ = nullptr, *mix_in_ = nullptr, *lr_out_ = nullptr, *gu_buf_ = nullptr, *act_ = nullptr,
        *head_in_ = nullptr;
@@ -215,6 +217,7 @@ class Zudatar : public ModelImpl {
     RUN(oalloc(&bigram_, static_cast<size_t>(buckets_ + 1) * W)); needed_.insert("bigram");
     RUN(valloc(&final_norm_, W, "final.norm"));
     RUN(dalloc(&last_token_, S, sizeof(int32_t), true));
+    size_t m_kv = 0, m_cd = 0;
     size_t m_proj = 8, m_q = 8, m_cq = 8, m_lat = 8, m_mix = 8, m_ch = 1, m_hd = 1, m_hv = 1, m_ff = 0;
     state_.resize(layers_.size());
     const size_t rows = static_cast<size_t>(lim.num_blocks) * lim.block_size;
@@ -251,6 +254,8 @@ class Zudatar : public ModelImpl {
         RUN(oalloc(&L.uq, HD * L.q_rank)); needed_.insert(a + "uq");
         RUN(oalloc(&L.ukT, HD * L.kv_rank)); needed_.insert(a + "uk");
         RUN(oalloc(&L.uv, HV * L.kv_rank)); needed_.insert(a + "uv");
+        RUN(oalloc(&L.ukv, (HD + HV) * L.kv_rank));
+        m_kv = std::max(m_kv, HD + HV); m_cd = std::max<size_t>(m_cd, L.cache_row());
         RUN(valloc(&L.sink, L.H, a + "sink"));
         if (L.own_latent()) {
           needed_.insert(a + "dkv");
@@ -284,6 +289,7 @@ class Zudatar : public ModelImpl {
     RUN(oalloc(&mix_in_, T * m_mix)); RUN(dalloc(&conv_out_, T * m_ch)); RUN(dalloc(&decay_, T * m_hd)); RUN(dalloc(&gate_, T * m_hv));
     RUN(dalloc(&y_, T * m_hv));
     if (m_ff > 0) { RUN(oalloc(&gu_buf_, T * 2 * m_ff)); RUN(oalloc(&act_, T * m_ff)); }
+    if (m_kv > 0) { RUN(oalloc(&kv_, T * m_kv)); RUN(oalloc(&c_dense_, T * m_cd, true)); }
     NVLLM_CUDA(cudaStreamSynchronize(stream));
     return 0;
   }
@@ -407,7 +413,12 @@ class Zudatar : public ModelImpl {
       NVLLM_CHECK_ARG(rows * cols == t.rows * t.cols && (t.kind == 1 || (rows == t.rows && cols == t.cols)), NVLLM_ERR_ARG,
                       "load_weight(%s): expected [%lld, %lld], got [%lld, %lld]", name_c, (long long)t.rows, (long long)t.cols, (long long)rows,
                       (long long)cols);
-      if (t.kind == 0) RUN(put(t.dst, t.off, src, rows, cols, st));
+      if (t.kind == 0) {
+        RUN(put(t.dst, t.off, src, rows, cols, st));
+        const Layer& L0 = name[0] == 'l' ? layers_[atoi(name.substr(1).c_str())] : layers_[0];
+        if (name[0] == 'l' && L0.mix == kLatent && t.dst == L0.uv)   // the value map also sits below the key map
+          RUN(put(L0.ukv, static_cast<size_t>(L0.H) * L0.D * L0.kv_rank, src, rows, cols, st));
+      }
       else if (t.kind == 1) RUN(putf(static_cast<float*>(t.dst), src, rows * cols, t.scale, st));
       else if (t.kind == 4) RUN(putf(static_cast<float*>(t.dst) + t.off * cols, src, rows * cols, 1.f, st));
       else {  // key map [H * D, R] -> per head [R, D]: the query is folded through it, q_abs_h = Uk_h^T q_h
@@ -418,6 +429,7 @@ class Zudatar : public ModelImpl {
             for (int r = 0; r < L.kv_rank; ++r)
               tr[(static_cast<size_t>(h) * L.kv_rank + r) * L.D + d] = src[(static_cast<size_t>(h) * L.D + d) * L.kv_rank + r];
         RUN(put(t.dst, 0, tr.data(), rows, cols, st));
+        RUN(put(L.ukv, 0, src, rows, cols, st));           // and as stored, above the value map
       }
     }
     loaded_.insert(name);
@@ -544,6 +556,24 @@ class Zudatar : public ModelImpl {
           mk("rms_norm_rows (kv latent -> cache)");
         }
         RUN(lin(q_, cq_, L.uq, HD, L.q_rank, L.q_rank, HD, dt_, "query up-projection"));
+        // Whole prompts (every sequence starts at position 0, so all keys are the step's own tokens): keys and values per head
+        // are computed from the step's latents and the layer runs as ordinary windowed attention over them — a fraction of the
+        // folded form's work (a key costs dim + vdim multiply-adds per head instead of 2 kv_rank).  Portions and single tokens
+        // take the folded form below, which reads nothing but the cached latents.
+        if (v.whole_prompts && dt_ == NVLLM_BF16 && knobs().latent_unfold && N >= 256 && L.D % 8 == 0 && L.V % 8 == 0 && L.D <= 128 && L.V <= 128) {
+          const int row = L.cache_row(), kvn = HD + HV;
+          if (own) {
+            RUN(nvllm_rms_norm_rows(c_dense_, row, proj_ + L.q_rank, ldl, L.dkv_norm, nullptr, N, R, eps_, dt_, st)); ++launches; mk("rms_norm_rows (kv latent, dense)");
+          } else {
+            RUN(nvllm_gather_rows(c_dense_, cache, v.slots, N, row, lim_.num_blocks * lim_.block_size, dt_, st)); ++launches; mk("gather_rows (cached latents)");
+          }
+          RUN(lin(kv_, c_dense_, L.ukv, kvn, R, row, kvn, dt_, "key / value up-projection"));
+          RUN(nvllm_window_attention(mix_in_, HV, q_, HD, proj_ + L.q_rank + own, ldl, 1, kv_, off(kv_, HD), kvn, kvn, v.tok_seq, v.positions, nullptr,
+                                     v.table_cap, lim_.block_size, N, L.H, L.H, L.D, L.V, L.scale, 0.f, 0.f, 1, L.window, L.sink, v.cu_tokens, S, dt_, st));
+          ++launches; mk("window_attention (latent layer, whole prompts)");
+          RUN(lin(sub_out_, mix_in_, L.o, W, HV, HV, W, dt_, "mixer output projection"));
+          goto mixer_done;
+        }
         // Per-head projections: with many tokens every head is a tensor-core GEMM of its own; with few (decoding) one batched
         // launch of the tile kernel beats `heads` launch latencies.
         const bool head_gemms = dt_ == NVLLM_BF16 && N >= 512 && L.D % 64 == 0 && R % 64 == 0 && L.V % 8 == 0 && HD % 8 == 0 && L.D % 8 == 0;
@@ -587,6 +617,7 @@ class Zudatar : public ModelImpl {
         RUN(nvllm_gated_group_norm_act(mix_in_, HV, y_, HV, gate_, HV, L.o_norm, 1, N, HV, L.H, eps_, 0, 1, dt_, st)); ++launches; mk("gated_group_norm");
       }
       RUN(lin(sub_out_, mix_in_, L.o, W, HV, HV, W, dt_, "mixer output projection"));
+    mixer_done:
       if (L.has_mlp) {
         RUN(norm(sub_out_, L.norm1b, L.norm2));
         if (dt_ == NVLLM_BF16 && L.ff % 128 == 0 && W % 64 == 0) {  // SiLU gate in the GEMM's epilogue: [N, 2 ff] never reaches HBM

@@ -581,6 +581,30 @@ def test_engine_schedules_match_the_oracle(cuda, tmp_path, name, dtype):
         assert rel_err(dec[i], whole[i].astype(np.float64)).max() < (1e-4 if dtype == "float32" else 0.2)
 
 
+@pytest.mark.parametrize("name", ["tensor_core", "all_kinds"])
+def test_whole_prompts_of_latent_layers_unfolded(cuda, tmp_path, monkeypatch, name):
+    """Long whole prompts (bf16): a latent-attention layer computes keys and values per head from the step's latents and runs
+    as windowed attention over them; the folded form (forced by the switch, and always taken by portions and single tokens)
+    gives the same logits to rounding, and both match the oracle.  Two prompts in one step, windows shorter than the prompts."""
+    rng = np.random.default_rng(31)
+    cfg = variant(name)
+    w = weights_for(cfg, rng)
+    reqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (300, 270)]
+    ref = [Z.run_sequence(cfg, w, r) for r in reqs]
+    eng, _ = make_engine(tmp_path, cfg, w, "bfloat16", bs=16, blocks=40)
+    both = replay(eng, reqs, [[(0, 300), (1, 270)]])
+    monkeypatch.setenv("NVLLM_LATENT_UNFOLD", "0")
+    folded = replay(eng, reqs, [[(0, 300), (1, 270)]])
+    monkeypatch.delenv("NVLLM_LATENT_UNFOLD")
+    cut_up = replay(eng, reqs, [[(0, 150), (1, 270)], [(0, 150)]])       # request 0 continues from its cache: the folded form
+    for i in range(2):
+        assert within(rel_err(both[i], ref[i]), "bfloat16"), (i, rel_err(both[i], ref[i]).max())
+        assert within(rel_err(folded[i], ref[i]), "bfloat16")
+        assert rel_err(both[i], folded[i].astype(np.float64)).max() < 0.2 and rel_err(cut_up[i], both[i].astype(np.float64)).max() < 0.2
+    if name == "tensor_core":
+        assert not np.array_equal(both[0], folded[0])      # the two forms really are different code paths
+
+
 def test_engine_layer_taps_match_the_oracle(cuda, tmp_path):
     """The residual stream after every layer, for a prompt: each mixer kind is checked where it sits, not only at the logits."""
     rng = np.random.default_rng(21)
