@@ -825,6 +825,9 @@ def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
         out["latent_window_attention"] = (4 * wpairs * H * R, keys_read * R * 2 + n_tok * H * R * 6)
         out["value up-projection (per-head GEMMs)"] = out["value up-projection (per-head linear)"] = (2 * n_tok * H * V * R, 2 * H * V * R + n_tok * H * 2 * (R + V))
         out["mixer output projection"] = gemm(W, H * V)
+        # whole prompts of a latent layer: keys and values per head from the step's latents, then windowed attention over them
+        out["key / value up-projection"] = gemm(H * (D + V), R)
+        out["window_attention (latent layer, whole prompts)"] = (2 * wpairs * H * (D + V), n_tok * H * (D + V) * 2 + n_tok * H * (D + V) * 2)
         ch = 2 * dG * dD + dH * dV
         out["delta q k v b projection"] = gemm(ch + dH, W)
         out["delta decay / gate first step"] = gemm(2 * lr, W)

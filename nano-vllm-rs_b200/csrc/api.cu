@@ -58,6 +58,7 @@ static void parse_knobs() {
   k.capped_mma = num("NVLLM_CAPPED_MMA", 1);
   k.linear_mma = num("NVLLM_LINEAR_MMA", 1);
   k.latent_unfold = num("NVLLM_LATENT_UNFOLD", 1);
+  k.delta_cfg = num("NVLLM_DELTA_CFG", 0);
   k.ar_ll = num("NVLLM_AR_LL", 1);
   k.gemm_push = num("NVLLM_GEMM_PUSH", 0);
   k.decode_persist = num("NVLLM_DECODE_PERSIST", 0);

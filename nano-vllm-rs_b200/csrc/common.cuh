@@ -71,6 +71,7 @@ struct Knobs {
   int ar_ll = 1;            // NVLLM_AR_LL: 0 = always the flag-protocol fused all-reduce (no low-latency push variant)
   long long ar_ll_max_bytes = 8ll << 20;  // NVLLM_AR_LL_MAX_BYTES: largest message of the low-latency variant (6x this is reserved)
   int latent_mma = 1;       // NVLLM_LATENT_MMA: 0 = latent attention always on the CUDA-core kernel (A/B against the tensor-core one)
+  int delta_cfg = 0;        // NVLLM_DELTA_CFG: alternative thread layouts of the gated delta rule for key sizes 65..128
   int latent_unfold = 1;    // NVLLM_LATENT_UNFOLD: 0 = whole prompts of a latent-attention layer also take the folded (multi-query) form
   int linear_mma = 1;       // NVLLM_LINEAR_MMA: 0 = batched / odd-sized bf16 products always on the CUDA-core tile kernel
   int capped_mma = 1;       // NVLLM_CAPPED_MMA: 0 = capped attention always on the CUDA-core kernel (A/B against the tensor-core one)
