@@ -527,12 +527,15 @@ int nvllm_window_attention(void* out, int64_t ldo, const void* q, int64_t ldq, c
                            float softcap, float temp_coef, int32_t temp_every, int32_t window, const float* sinks,
                            const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream);
 /* nvllm_latent_attention with a sliding window (window > 0: keys p - window + 1 .. p), sinks (f32 [heads], nullable, as
- * above) and a gate per head (f32 [n, heads], ldg apart, nullable: out[t, h, :] *= sigmoid(gate[t, h])). */
+ * above) and a gate per head (f32 [n, heads], ldg apart, nullable: out[t, h, :] *= sigmoid(gate[t, h])).
+ * workspace (nullable, f32): with it, single tokens in a long window (1000 keys and more) whose CTAs would not fill the SMs
+ * split their key tiles over up to 4 CTAs; needs n * heads * 4 * (kv_rank + 2) * 4 bytes for n <= 256 (larger batches never split). */
 int nvllm_latent_window_attention(void* out, int64_t ldo, const float* q_abs, int64_t ldqa, const void* q, int64_t ldq,
                                   const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
                                   int32_t table_cap, int32_t block_size, const void* cache, int64_t cache_row, int32_t n,
                                   int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale, int32_t window,
-                                  const float* sinks, const float* gate, int64_t ldg, int32_t dtype, void* stream);
+                                  const float* sinks, const float* gate, int64_t ldg, void* workspace, size_t workspace_bytes,
+                                  int32_t dtype, void* stream);
 /* Per-token preparation of the gated delta rule, in place, all f32:
  *   q, k: [n, groups * dk] -> every head divided by sqrt(sum of squares + unit_eps), q also times q_scale;
  *   beta: [n, heads] -> sigmoid;   decay: [n, heads * dk] -> exp(-exp(a_log[h]) * softplus(decay + dt_bias[h, c])). */

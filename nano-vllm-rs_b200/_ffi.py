@@ -113,7 +113,7 @@ PROTOTYPES = {
     "nvllm_window_attention": (i32, [vp, i64, vp, i64, vp, i64, i32, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                      f32, f32, f32, i32, i32, vp, vp, i32, i32, vp]),
     "nvllm_latent_window_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp, i64, i32, i32, i32, i32, i32, f32, i32,
-                                            vp, vp, i64, i32, vp]),
+                                            vp, vp, i64, vp, sz, i32, vp]),
     "nvllm_delta_prepare": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, i32, i32, i32, i32, f32, f32, vp]),
     "nvllm_gated_delta_recurrence": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                                            vp]),

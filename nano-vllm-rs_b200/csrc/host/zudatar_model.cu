@@ -105,6 +105,7 @@ class Zudatar : public ModelImpl {
   std::map<std::pair<double, int>, float*> rope_tables_;
   // activations
   float *h_ = nullptr, *proj_ = nullptr, *q_abs_ = nullptr, *conv_out_ = nullptr, *decay_ = nullptr, *gate_ = nullptr, *y_ = nullptr;
+  float* lat_ws_ = nullptr; size_t lat_ws_bytes_ = 0;   // partial softmaxes of single tokens whose keys are split over CTAs
   void *kv_ = nullptr, *c_dense_ = nullptr;   // whole prompts of a latent layer: the step's latents and their keys / values per head
   void *sub_out_ = nullptr;   // a sublayer's output in the operand type; its norm and the residual sum are f32
   void *normed_ = nullptr, *q_ = nullptr, *cq_ = nullptr, *o_lat_ = nullptr, *mix_in_ = nullptr, *lr_out_ = nullptr, *gu_buf_ = nullptr, *act_ = nullptr,
@@ -289,7 +290,11 @@ class Zudatar : public ModelImpl {
     RUN(oalloc(&mix_in_, T * m_mix)); RUN(dalloc(&conv_out_, T * m_ch)); RUN(dalloc(&decay_, T * m_hd)); RUN(dalloc(&gate_, T * m_hv));
     RUN(dalloc(&y_, T * m_hv));
     if (m_ff > 0) { RUN(oalloc(&gu_buf_, T * 2 * m_ff)); RUN(oalloc(&act_, T * m_ff)); }
-    if (m_kv > 0) { RUN(oalloc(&kv_, T * m_kv)); RUN(oalloc(&c_dense_, T * m_cd, true)); }
+    if (m_kv > 0) {
+      RUN(oalloc(&kv_, T * m_kv)); RUN(oalloc(&c_dense_, T * m_cd, true));
+      lat_ws_bytes_ = std::min<size_t>(T, 256) * 4 * (m_lat + 2 * 64) * sizeof(float);   // (tokens <= 256) x heads x 4 splits x (kv_rank + 2)
+      RUN(dalloc(&lat_ws_, lat_ws_bytes_ / sizeof(float)));
+    }
     NVLLM_CUDA(cudaStreamSynchronize(stream));
     return 0;
   }
@@ -588,7 +593,7 @@ class Zudatar : public ModelImpl {
           mk("q absorb (per-head linear)");
         }
         RUN(nvllm_latent_window_attention(o_lat_, HR, q_abs_, HR, nullptr, 0, v.tok_seq, v.positions, v.tables, v.table_cap, lim_.block_size, cache,
-                                          L.cache_row(), N, L.H, L.D, 0, R, L.scale, L.window, L.sink, proj_ + L.q_rank + own, ldl, dt_, st));
+                                          L.cache_row(), N, L.H, L.D, 0, R, L.scale, L.window, L.sink, proj_ + L.q_rank + own, ldl, lat_ws_, lat_ws_bytes_, dt_, st));
         ++launches; mk("latent_window_attention");
         if (head_gemms) {
           for (int hh = 0; hh < L.H; ++hh) {

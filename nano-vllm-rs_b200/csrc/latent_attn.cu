@@ -99,6 +99,7 @@ struct AttnArgs {
   int n, heads, dim, rot_dim, kv_rank;
   float scale;
   int window; const float* sinks; const float* gate; int64_t ldg;   // 0 / null: none
+  int splits; float* part;   // splits > 1: CTAs along z share a token's key tiles; partial (acc[kv_rank], m, l) per (token, head, split)
 };
 
 constexpr int kKeyTile = 32;
@@ -259,6 +260,15 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
       if (tq[q] >= 0) jstart = lo[q] < jstart ? lo[q] : jstart;
     }
     jstart &= ~(kMmaKeys - 1);   // key tiles stay anchored at multiples of 64 from the sequence's start
+    if (a.splits > 1) {          // this CTA's share of the tiles (single tokens with few CTAs: the keys are split along z)
+      const int tiles = (nkeys - jstart + kMmaKeys - 1) / kMmaKeys, per = (tiles + a.splits - 1) / a.splits;
+      jstart += static_cast<int>(blockIdx.z) * per * kMmaKeys;
+      const int jend = jstart + per * kMmaKeys;
+      nkeys = nkeys < jend ? nkeys : jend;
+      if (jstart > nkeys) jstart = nkeys;
+#pragma unroll
+      for (int q = 0; q < TQ; ++q) nk[q] = nk[q] < nkeys ? nk[q] : nkeys;
+    }
     __syncthreads();   // previous pass done with every buffer; the zero fill above is ordered before the copies below
     if (tid < TQ * 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
     // four threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
@@ -434,6 +444,29 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
       }
       __syncthreads();   // tile, P and the row factors are free again
     }
+    if (a.splits > 1) {   // unnormalised partial results; latent_attn_merge_kernel finishes the softmax
+      cp_async_wait<0>();
+      __syncthreads();    // a share without tiles never entered the loop: its row statistics are still the initial ones
+#pragma unroll
+      for (int q = 0; q < TQ; ++q) {
+        if (tq[q] < 0) continue;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = g + 8 * half, h = hbase + r;
+          if (h >= a.heads) continue;
+          float* pr = a.part + ((static_cast<int64_t>(tq[q]) * a.heads + h) * a.splits + blockIdx.z) * (a.kv_rank + 2);
+#pragma unroll
+          for (int nt = 0; nt < 2 * NT2; ++nt)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int col = warp * RC + nt * 8 + 2 * t4 + c;
+              if (col < a.kv_rank) pr[col] = acc[q][nt][2 * half + c];
+            }
+          if (warp == 0 && t4 == 0) { pr[a.kv_rank] = m_s[q * 16 + r]; pr[a.kv_rank + 1] = l_s[q * 16 + r]; }
+        }
+      }
+      continue;
+    }
 #pragma unroll
     for (int q = 0; q < TQ; ++q) {
       if (tq[q] < 0) continue;
@@ -462,6 +495,34 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
   }
 }
 
+// One warp per (token, head): merges the splits' partial softmaxes, adds the sink to the denominator, applies the gate.
+__global__ void __launch_bounds__(128) latent_attn_merge_kernel(const AttnArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (item >= static_cast<int64_t>(a.n) * a.heads) return;
+  const int64_t t = item / a.heads;
+  const int h = static_cast<int>(item - t * a.heads), W = a.kv_rank + 2;
+  const float* pr = a.part + item * a.splits * W;
+  float mx = a.sinks ? a.sinks[h] : -INFINITY;
+  for (int s = 0; s < a.splits; ++s) mx = fmaxf(mx, pr[s * W + a.kv_rank]);
+  float den = a.sinks ? expf(a.sinks[h] - mx) : 0.f;
+  for (int s = 0; s < a.splits; ++s) {
+    const float ms = pr[s * W + a.kv_rank];
+    if (ms != -INFINITY) den += expf(ms - mx) * pr[s * W + a.kv_rank + 1];
+  }
+  float inv = den > 0.f ? 1.0f / den : 0.f;
+  if (a.gate) inv *= 1.0f / (1.0f + expf(-a.gate[t * a.ldg + h]));
+  bf16* out = static_cast<bf16*>(a.out) + t * a.ldo + static_cast<int64_t>(h) * a.kv_rank;
+  for (int c = lane; c < a.kv_rank; c += 32) {
+    float v = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+      const float ms = pr[s * W + a.kv_rank];
+      if (ms != -INFINITY) v = fmaf(expf(ms - mx), pr[s * W + c], v);
+    }
+    out[c] = __float2bfloat16_rn(v * inv);
+  }
+}
+
 template <int NT2, int TQ>
 int launch_attn_mma_tq(const AttnArgs& a, cudaStream_t st) {
   const int DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 128;
@@ -469,9 +530,13 @@ int launch_attn_mma_tq(const AttnArgs& a, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(TQ * 16 + 2 * kMmaKeys) * DPS * 2 + TQ * 16 * kPsStride * 2 +
                       (TQ * 2 * 16 * kSsStride + TQ * 48) * 4;
   NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2, TQ>), 225 * 1024);
-  dim3 grid((a.n + TQ - 1) / TQ, (a.heads + 15) / 16);
+  dim3 grid((a.n + TQ - 1) / TQ, (a.heads + 15) / 16, TQ == 1 && a.splits > 1 ? a.splits : 1);
   latent_attn_mma_kernel<NT2, TQ><<<grid, kMmaThreads, smem, st>>>(a, DPS, DP16);
   NVLLM_LAUNCH_CHECK("latent_attn_mma_kernel");
+  if (TQ == 1 && a.splits > 1) {
+    latent_attn_merge_kernel<<<static_cast<unsigned>((static_cast<int64_t>(a.n) * a.heads + 3) / 4), 128, 0, st>>>(a);
+    NVLLM_LAUNCH_CHECK("latent_attn_merge_kernel");
+  }
   return 0;
 }
 
@@ -482,7 +547,7 @@ int launch_attn_mma(const AttnArgs& a, cudaStream_t st) {
   const int DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 128;
   const int DPS = (DP16 > RP ? DP16 : RP) + 8;
   const size_t smem2 = static_cast<size_t>(32 + 2 * kMmaKeys) * DPS * 2 + 32 * kPsStride * 2 + (4 * 16 * kSsStride + 96) * 4;
-  if (a.n > 256 && knobs().latent_mma != 2 && smem2 <= 225 * 1024) return launch_attn_mma_tq<NT2, 2>(a, st);
+  if (a.n > 256 && knobs().latent_mma != 2 && smem2 <= 225 * 1024) { AttnArgs b = a; b.splits = 1; return launch_attn_mma_tq<NT2, 2>(b, st); }
   return launch_attn_mma_tq<NT2, 1>(a, st);
 }
 
@@ -537,31 +602,44 @@ extern "C" int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs
                                       int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale,
                                       int32_t dtype, void* stream) {
   return nvllm_latent_window_attention(out, ldo, q_abs, ldqa, q, ldq, tok_seq, positions, block_tables, table_cap, block_size, cache,
-                                       cache_row, n, heads, dim, rot_dim, kv_rank, scale, 0, nullptr, nullptr, 0, dtype, stream);
+                                       cache_row, n, heads, dim, rot_dim, kv_rank, scale, 0, nullptr, nullptr, 0, nullptr, 0, dtype, stream);
 }
 
 extern "C" int nvllm_latent_window_attention(void* out, int64_t ldo, const float* q_abs, int64_t ldqa, const void* q, int64_t ldq,
                                              const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
                                              int32_t table_cap, int32_t block_size, const void* cache, int64_t cache_row, int32_t n,
                                              int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale,
-                                             int32_t window, const float* sinks, const float* gate, int64_t ldg, int32_t dtype,
-                                             void* stream) {
+                                             int32_t window, const float* sinks, const float* gate, int64_t ldg, void* workspace,
+                                             size_t workspace_bytes, int32_t dtype, void* stream) {
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && dim >= 0 && rot_dim >= 0 && kv_rank > 0 && kv_rank <= 1024 && table_cap > 0 && block_size > 0,
                   NVLLM_ERR_ARG, "latent_attention: sizes (kv_rank <= 1024)");
   NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "latent_attention: dtype %d", dtype);
   if (n == 0) return 0;
   NVLLM_CHECK_ARG(out && q_abs && (q || rot_dim == 0) && tok_seq && positions && block_tables && cache, NVLLM_ERR_ARG, "latent_attention: NULL");
   const AttnArgs a{out, ldo, q_abs, ldqa, q ? q : q_abs, ldq, tok_seq, positions, block_tables, table_cap, block_size, cache, cache_row,
-                   n, heads, dim, rot_dim, kv_rank, scale, window > 0 ? window : 0, sinks, gate, ldg};
+                   n, heads, dim, rot_dim, kv_rank, scale, window > 0 ? window : 0, sinks, gate, ldg, 1, static_cast<float*>(workspace)};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 caches with a 16-byte row pitch and kv_rank <= 512 run on the tensor cores (NVLLM_LATENT_MMA=0: the CUDA-core kernel)
   const int dp16 = (static_cast<int>(cache_row) + 15) / 16 * 16;
   if (dtype == NVLLM_BF16 && knobs().latent_mma != 0 && kv_rank <= 512 && cache_row % 8 == 0 && dp16 <= 704 &&
       (reinterpret_cast<uintptr_t>(cache) & 15u) == 0) {
-    if (kv_rank <= 128) return launch_attn_mma<1>(a, st);
-    if (kv_rank <= 256) return launch_attn_mma<2>(a, st);
-    if (kv_rank <= 384) return launch_attn_mma<3>(a, st);
-    return launch_attn_mma<4>(a, st);
+    // Single tokens with a bounded key range (a window) and fewer CTAs than SMs: split every token's key tiles over up to 4
+    // CTAs, as many as fill the SMs once and leave each at least eight tiles; the partials meet in latent_attn_merge_kernel.
+    // (Measured, 64 tokens x 16 heads, rank 512: a window of 2048 keys 118 -> 79 us; at 512 keys the second launch costs what
+    // the shorter loop saves, 39 -> 37 us, so short windows stay on one CTA.)
+    AttnArgs b = a;
+    if (workspace != nullptr && n <= 256 && window > 0) {
+      const int64_t ctas = static_cast<int64_t>(n) * ((heads + 15) / 16);
+      int splits = static_cast<int>(sm_count() / (ctas > 0 ? ctas : 1));
+      const int tiles = (window + 2 * kMmaKeys - 2) / kMmaKeys;   // tiles a window can touch
+      splits = splits > 4 ? 4 : splits;
+      splits = splits > tiles / 8 ? tiles / 8 : splits;
+      if (splits > 1 && static_cast<size_t>(n) * heads * splits * (kv_rank + 2) * sizeof(float) <= workspace_bytes) b.splits = splits;
+    }
+    if (kv_rank <= 128) return launch_attn_mma<1>(b, st);
+    if (kv_rank <= 256) return launch_attn_mma<2>(b, st);
+    if (kv_rank <= 384) return launch_attn_mma<3>(b, st);
+    return launch_attn_mma<4>(b, st);
   }
   return dtype == NVLLM_BF16 ? dispatch_attn<bf16>(a, st) : dispatch_attn<float>(a, st);
 }

@@ -537,14 +537,14 @@ def window_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, bloc
 
 
 def latent_window_attention(q_abs, tok_seq, positions, tables, block_size, cache, heads, kv_rank, scale, dtype, window=0, sinks=None,
-                            gate=None):
+                            gate=None, workspace=None):
     """q_abs f32 [n, heads * kv_rank] (the key map folded into the query); cache [slots, row >= kv_rank] in `dtype`."""
     n = q_abs.shape[0]
     out = torch.empty((n, heads * kv_rank), dtype=dtype, device=q_abs.device)
     check(_ffi.lib().nvllm_latent_window_attention(_p(out), out.stride(0), _p(q_abs), q_abs.stride(0), None, 0, _p(tok_seq), _p(positions),
                                                    _p(tables), tables.shape[1], block_size, _p(cache), cache.stride(0), n, heads, 0, 0,
                                                    kv_rank, scale, window, _p(sinks), _p(gate), gate.stride(0) if gate is not None else 0,
-                                                   _dt(out), _stream()))
+                                                   _p(workspace), workspace.numel() * 4 if workspace is not None else 0, _dt(out), _stream()))
     return out
 
 

@@ -314,6 +314,40 @@ def test_latent_window_attention(cuda, dtype, case):
     np.testing.assert_allclose(out.float().cpu().numpy().reshape(n, H, R), ref, rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("window", [1000, 1100, 64, 5000])
+@pytest.mark.parametrize("H,R", [(3, 24), (20, 64)])
+def test_latent_window_attention_splits_keys_of_single_tokens(cuda, window, H, R):
+    """Few single tokens (bf16): with a workspace every token's key tiles are split over several CTAs and merged; the result is
+    the unsplit kernel's to rounding and the oracle's.  Contexts shorter than a tile, at tile borders, and longer than the window."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(window + H)
+    ctx, bs = [300, 65, 3, 1100, 64, 1517, 1], 16
+    tables, slot, nslots = _paged(rng, ctx, bs)
+    C = [Z.bf16_round(rng.standard_normal((c, R))) for c in ctx]
+    cache = np.zeros((nslots, R))
+    for s, c in enumerate(ctx):
+        for p in range(c):
+            cache[slot(s, p)] = C[s][p]
+    n = len(ctx)
+    pos = np.array(ctx) - 1
+    qa = Z.bf16_round(rng.standard_normal((n, H, R)))
+    gate, sinks = rng.standard_normal((n, H)), rng.standard_normal(H) + 1.0
+    scale = 0.7 / np.sqrt(R)
+    ref = np.zeros((n, H, R))
+    for t in range(n):
+        Cs = C[t][max(0, pos[t] - window + 1):pos[t] + 1]
+        for h in range(H):
+            ref[t, h] = (Z.window_softmax((Cs @ qa[t, h]) * scale, f32r(sinks)[h]) @ Cs) * Z.sigmoid(f32r(gate)[t, h])
+    args = (dev_t(qa.reshape(n, -1), cuda), dev_i(np.arange(n), cuda), dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs,
+            dev_t(cache, cuda, torch.bfloat16), H, R, scale, torch.bfloat16, window, dev_t(sinks, cuda), dev_t(gate, cuda))
+    plain = ops.latent_window_attention(*args).float().cpu().numpy().reshape(n, H, R)
+    ws = torch.full((n * H * 4 * (R + 2),), float("nan"), device=cuda)
+    split = ops.latent_window_attention(*args, workspace=ws).float().cpu().numpy().reshape(n, H, R)
+    assert torch.isnan(ws[:n * H * 2 * (R + 2)]).all() == (window < 1000)     # long windows used the workspace
+    np.testing.assert_allclose(split, ref, rtol=2e-2, atol=2e-2)
+    np.testing.assert_allclose(split, plain, rtol=1e-2, atol=1e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_tok", [1, 300])
 def test_latent_window_edges_stand_out(cuda, dtype, n_tok):
@@ -723,7 +757,7 @@ def test_generation_survives_preemption(cuda, tmp_path):
 
 def test_synthetic_weights_and_command_line(cuda, tmp_path):
     """Seeded synthetic weights (no checkpoint) run a step; `python -m nano_vllm_rs_b200 generate` on a checkpoint gives the
-    oracle's greedy tokens; the registry lists the architecture."""
+    oracle's greedy tokens and, with a temperature, draws of the device sampler; the registry lists the architecture."""
     import sys
     from nano_vllm_rs_b200.engine import Config, LLMEngine, SamplingParams
     rng = np.random.default_rng(26)
@@ -737,8 +771,10 @@ def test_synthetic_weights_and_command_line(cuda, tmp_path):
     w = weights_for(cfg, rng)
     _, model_dir = make_engine(tmp_path, cfg, w, "float32")
     prompt = rng.integers(0, cfg["vocab"], 9).tolist()
-    r = subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "generate", "--model", model_dir, "--dtype", "float32", "--prompt-ids",
-                        ",".join(map(str, prompt)), "--max-tokens", "12", "--block-size", "16"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    run = lambda *extra: subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "generate", "--model", model_dir, "--dtype", "float32", "--prompt-ids",
+                                         ",".join(map(str, prompt)), "--max-tokens", "12", "--block-size", "16", *extra], cwd=ROOT, capture_output=True,
+                                        text=True, timeout=600)
+    r = run()
     assert r.returncode == 0, r.stderr[-2000:]
     out = json.loads(r.stdout.strip().splitlines()[-1])
     ref, margins = greedy(cfg, w, prompt, 12)
@@ -746,6 +782,10 @@ def test_synthetic_weights_and_command_line(cuda, tmp_path):
         if out["completion_ids"][j] != ref[j]:
             assert margins[j] < 1e-3
             break
+    r = run("--temperature", "1.5", "--top-k", "20")      # the device sampler draws from the same logits
+    assert r.returncode == 0, r.stderr[-2000:]
+    sampled = json.loads(r.stdout.strip().splitlines()[-1])["completion_ids"]
+    assert len(sampled) == 12 and all(0 <= t < cfg["vocab"] for t in sampled) and sampled != ref
     r = subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "architectures"], cwd=ROOT, capture_output=True, text=True, timeout=120)
     assert "Zudatar" in r.stdout
 
