@@ -565,7 +565,12 @@ class Zudatar : public ModelImpl {
         // are computed from the step's latents and the layer runs as ordinary windowed attention over them — a fraction of the
         // folded form's work (a key costs dim + vdim multiply-adds per head instead of 2 kv_rank).  Portions and single tokens
         // take the folded form below, which reads nothing but the cached latents.
-        if (v.whole_prompts && dt_ == NVLLM_BF16 && knobs().latent_unfold && N >= 256 && L.D % 8 == 0 && L.V % 8 == 0 && L.D <= 128 && L.V <= 128) {
+        const bool unfolded = v.whole_prompts && dt_ == NVLLM_BF16 && knobs().latent_unfold && N >= 256 && L.D % 8 == 0 && L.V % 8 == 0 &&
+                              L.D <= 128 && L.V <= 128;
+        // Per-head projections of the folded form: with many tokens every head is a tensor-core GEMM of its own; with few
+        // (decoding) one batched launch of the mma.sync tile kernel beats `heads` launch latencies.
+        const bool head_gemms = dt_ == NVLLM_BF16 && N >= 512 && L.D % 64 == 0 && R % 64 == 0 && L.V % 8 == 0 && HD % 8 == 0 && L.D % 8 == 0;
+        if (unfolded) {
           const int row = L.cache_row(), kvn = HD + HV;
           if (own) {
             RUN(nvllm_rms_norm_rows(c_dense_, row, proj_ + L.q_rank, ldl, L.dkv_norm, nullptr, N, R, eps_, dt_, st)); ++launches; mk("rms_norm_rows (kv latent, dense)");
@@ -576,34 +581,31 @@ class Zudatar : public ModelImpl {
           RUN(nvllm_window_attention(mix_in_, HV, q_, HD, proj_ + L.q_rank + own, ldl, 1, kv_, off(kv_, HD), kvn, kvn, v.tok_seq, v.positions, nullptr,
                                      v.table_cap, lim_.block_size, N, L.H, L.H, L.D, L.V, L.scale, 0.f, 0.f, 1, L.window, L.sink, v.cu_tokens, S, dt_, st));
           ++launches; mk("window_attention (latent layer, whole prompts)");
-          RUN(lin(sub_out_, mix_in_, L.o, W, HV, HV, W, dt_, "mixer output projection"));
-          goto mixer_done;
-        }
-        // Per-head projections: with many tokens every head is a tensor-core GEMM of its own; with few (decoding) one batched
-        // launch of the tile kernel beats `heads` launch latencies.
-        const bool head_gemms = dt_ == NVLLM_BF16 && N >= 512 && L.D % 64 == 0 && R % 64 == 0 && L.V % 8 == 0 && HD % 8 == 0 && L.D % 8 == 0;
-        if (head_gemms) {
-          for (int hh = 0; hh < L.H; ++hh) {
-            RUN(nvllm_gemm_bf16(q_abs_ + static_cast<size_t>(hh) * R, off(q_, static_cast<size_t>(hh) * L.D), off(L.ukT, static_cast<size_t>(hh) * R * L.D),
-                                N, R, L.D, HD, L.D, HR, NVLLM_F32, nullptr, 0, st)); ++launches;
-          }
-          mk("q absorb (per-head GEMMs)");
         } else {
-          RUN(nvllm_linear(q_abs_, q_, L.ukT, N, R, L.D, HD, L.D, HR, L.H, L.D, static_cast<int64_t>(R) * L.D, R, dt_, NVLLM_F32, st)); ++launches;
-          mk("q absorb (per-head linear)");
-        }
-        RUN(nvllm_latent_window_attention(o_lat_, HR, q_abs_, HR, nullptr, 0, v.tok_seq, v.positions, v.tables, v.table_cap, lim_.block_size, cache,
-                                          L.cache_row(), N, L.H, L.D, 0, R, L.scale, L.window, L.sink, proj_ + L.q_rank + own, ldl, lat_ws_, lat_ws_bytes_, dt_, st));
-        ++launches; mk("latent_window_attention");
-        if (head_gemms) {
-          for (int hh = 0; hh < L.H; ++hh) {
-            RUN(nvllm_gemm_bf16(off(mix_in_, static_cast<size_t>(hh) * L.V), off(o_lat_, static_cast<size_t>(hh) * R),
-                                off(L.uv, static_cast<size_t>(hh) * L.V * R), N, L.V, R, HR, R, HV, NVLLM_BF16, nullptr, 0, st)); ++launches;
+          if (head_gemms) {
+            for (int hh = 0; hh < L.H; ++hh) {
+              RUN(nvllm_gemm_bf16(q_abs_ + static_cast<size_t>(hh) * R, off(q_, static_cast<size_t>(hh) * L.D), off(L.ukT, static_cast<size_t>(hh) * R * L.D),
+                                  N, R, L.D, HD, L.D, HR, NVLLM_F32, nullptr, 0, st)); ++launches;
+            }
+            mk("q absorb (per-head GEMMs)");
+          } else {
+            RUN(nvllm_linear(q_abs_, q_, L.ukT, N, R, L.D, HD, L.D, HR, L.H, L.D, static_cast<int64_t>(R) * L.D, R, dt_, NVLLM_F32, st)); ++launches;
+            mk("q absorb (per-head linear)");
           }
-          mk("value up-projection (per-head GEMMs)");
-        } else {
-          RUN(nvllm_linear(mix_in_, o_lat_, L.uv, N, L.V, R, HR, R, HV, L.H, R, static_cast<int64_t>(L.V) * R, L.V, dt_, dt_, st)); ++launches;
-          mk("value up-projection (per-head linear)");
+          RUN(nvllm_latent_window_attention(o_lat_, HR, q_abs_, HR, nullptr, 0, v.tok_seq, v.positions, v.tables, v.table_cap, lim_.block_size, cache,
+                                            L.cache_row(), N, L.H, L.D, 0, R, L.scale, L.window, L.sink, proj_ + L.q_rank + own, ldl, lat_ws_, lat_ws_bytes_,
+                                            dt_, st));
+          ++launches; mk("latent_window_attention");
+          if (head_gemms) {
+            for (int hh = 0; hh < L.H; ++hh) {
+              RUN(nvllm_gemm_bf16(off(mix_in_, static_cast<size_t>(hh) * L.V), off(o_lat_, static_cast<size_t>(hh) * R),
+                                  off(L.uv, static_cast<size_t>(hh) * L.V * R), N, L.V, R, HR, R, HV, NVLLM_BF16, nullptr, 0, st)); ++launches;
+            }
+            mk("value up-projection (per-head GEMMs)");
+          } else {
+            RUN(nvllm_linear(mix_in_, o_lat_, L.uv, N, L.V, R, HR, R, HV, L.H, R, static_cast<int64_t>(L.V) * R, L.V, dt_, dt_, st)); ++launches;
+            mk("value up-projection (per-head linear)");
+          }
         }
       } else {
         // [q | k | v | b] in one projection (f32 rows) and the first steps [a1 | g1] in another; the second steps; the
@@ -622,7 +624,6 @@ class Zudatar : public ModelImpl {
         RUN(nvllm_gated_group_norm_act(mix_in_, HV, y_, HV, gate_, HV, L.o_norm, 1, N, HV, L.H, eps_, 0, 1, dt_, st)); ++launches; mk("gated_group_norm");
       }
       RUN(lin(sub_out_, mix_in_, L.o, W, HV, HV, W, dt_, "mixer output projection"));
-    mixer_done:
       if (L.has_mlp) {
         RUN(norm(sub_out_, L.norm1b, L.norm2));
         if (dt_ == NVLLM_BF16 && L.ff % 128 == 0 && W % 64 == 0) {  // SiLU gate in the GEMM's epilogue: [N, 2 ff] never reaches HBM

@@ -526,11 +526,12 @@ def attn_rope_norm_store(proj, heads, kv_heads, dim, vdim, q_bias, k_bias, v_bia
 
 def window_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, block_size, heads, kv_heads, dim, vdim, scale, window=0,
                      sinks=None, gate_per_head=False, softcap=0.0, temp_coef=0.0, temp_every=1, cu_tokens=None):
+    """tables None (cu_tokens given): the keys are not paged, key j of sequence s is row cu_tokens[s] + j of k_cache / v_cache."""
     n = q.shape[0]
     out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
     check(_ffi.lib().nvllm_window_attention(_p(out), out.stride(0), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                             int(gate_per_head), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(tok_seq),
-                                            _p(positions), _p(tables), tables.shape[1], block_size, n, heads, kv_heads, dim, vdim, scale,
+                                            _p(positions), _p(tables), tables.shape[1] if tables is not None else 1, block_size, n, heads, kv_heads, dim, vdim, scale,
                                             softcap, temp_coef, temp_every, window, _p(sinks), _p(cu_tokens),
                                             cu_tokens.shape[0] - 1 if cu_tokens is not None else 0, _dt(q), _stream()))
     return out

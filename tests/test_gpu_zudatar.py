@@ -229,6 +229,31 @@ def test_window_attention_prompts_and_single_tokens(cuda, dtype, case):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,D,V,window", [(4, 4, 16, 8, 33), (6, 2, 32, 32, 64), (2, 1, 12, 20, 0), (3, 3, 128, 64, 100)])
+def test_window_attention_over_the_steps_own_rows(cuda, dtype, H, G, D, V, window):
+    """Whole prompts whose keys and values are not paged: key j of sequence s is row cu_tokens[s] + j of the key / value
+    matrices (no block tables), with sinks and head gates; three prompts of unequal length in one launch."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(H * D + window)
+    lens = [150, 1, 203]
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    n = int(cu[-1])
+    K, Vv = Z.bf16_round(rng.standard_normal((n, G, D))), Z.bf16_round(rng.standard_normal((n, G, V)))
+    q = Z.bf16_round(rng.standard_normal((n, H, D)))
+    gate, sinks = rng.standard_normal((n, H)), rng.standard_normal(H)
+    tok_seq = np.concatenate([[s] * l for s, l in enumerate(lens)]).astype(np.int32)
+    pos = np.concatenate([np.arange(l) for l in lens])
+    scale = 0.6 / np.sqrt(D)
+    ref = np.stack([_window_ref(q[t], K[cu[tok_seq[t]]:cu[tok_seq[t] + 1]], Vv[cu[tok_seq[t]]:cu[tok_seq[t] + 1]], H, G, scale, window, pos[t],
+                                f32r(sinks), f32r(gate)[t]) for t in range(n)])
+    kv = dev_t(np.concatenate([K.reshape(n, -1), Vv.reshape(n, -1)], axis=1), cuda, dtype)     # [K | V] side by side, as one projection writes them
+    out = ops.window_attention(dev_t(q.reshape(n, -1), cuda, dtype), dev_t(gate, cuda), kv, kv[:, G * D:], dev_i(tok_seq, cuda), dev_i(pos, cuda, torch.int64),
+                               None, 16, H, G, D, V, scale, window, dev_t(sinks, cuda), True, cu_tokens=dev_i(cu, cuda))
+    tol = 2e-2 if dtype == torch.bfloat16 else 3e-5
+    np.testing.assert_allclose(out.float().cpu().numpy().reshape(n, H, V), ref, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window,bs", [(70, 64), (5, 16), (64, 16), (130, 32)])
 def test_window_attention_edges_stand_out(cuda, dtype, window, bs):
     """One key is made to dominate: the last one inside the window must carry the output, the first one outside must not
