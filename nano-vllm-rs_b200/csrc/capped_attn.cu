@@ -106,6 +106,55 @@ __global__ void __launch_bounds__(128) attn_rope_norm_store_kernel(const RopeSto
   for (int c = lane; c < a.dim; c += 32) stv(dst + c, value(c) * r);
 }
 
+// The same with 16-byte accesses (dim a multiple of 4, at most 512; aligned rows): the head stays in registers, one pass.
+template <typename T>
+__global__ void __launch_bounds__(128) attn_rope_norm_store_vec_kernel(const RopeStoreArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = a.heads + a.kv_heads;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  if (item >= static_cast<int64_t>(a.n) * per) return;
+  const int t = static_cast<int>(item / per), hh = static_cast<int>(item % per);
+  const int32_t slot = a.slots[t];
+  const bool is_q = hh < a.heads;
+  const int h = is_q ? hh : hh - a.heads;
+  if (!is_q && slot < 0) return;
+  const float* src = a.proj + static_cast<int64_t>(t) * a.ldp + (is_q ? 0 : a.heads * a.dim) + static_cast<int64_t>(h) * a.dim;
+  const float* bias = is_q ? a.qb : a.kb;
+  if (bias) bias += static_cast<int64_t>(h) * a.dim;
+  int64_t pos = a.positions[t];
+  pos = pos < 0 ? 0 : (pos >= a.max_pos ? a.max_pos - 1 : pos);
+  const float2* tab = a.table + pos * (a.rot_dims / 2);
+  const int nv = a.dim / 4;
+  float4 v[4];
+  float sq = 0.f;
+  auto store4 = [](T* dst, const float4& o) {
+    if (sizeof(T) == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
+    else *reinterpret_cast<float4*>(dst) = o;
+  };
+  T* vd = (!is_q && a.v_from_k) ? static_cast<T*>(a.vc) + static_cast<int64_t>(slot) * a.v_row + static_cast<int64_t>(h) * a.vdim : nullptr;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < nv) {
+      float4 x = reinterpret_cast<const float4*>(src)[c];
+      if (bias) { const float4 b = reinterpret_cast<const float4*>(bias)[c]; x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w; }
+      if (vd) store4(vd + 4 * c, x);                       // the value is the key as projected
+      if (4 * c < a.rot_dims) { const float2 cs = tab[2 * c]; const float u = x.x, w = x.y; x.x = fmaf(u, cs.x, -w * cs.y); x.y = fmaf(w, cs.x, u * cs.y); }
+      if (4 * c + 2 < a.rot_dims) { const float2 cs = tab[2 * c + 1]; const float u = x.z, w = x.w; x.z = fmaf(u, cs.x, -w * cs.y); x.w = fmaf(w, cs.x, u * cs.y); }
+      v[k] = x;
+      sq += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  const float r = a.norm_eps > 0.f ? 1.0f / sqrtf(warp_sum(sq) / a.dim + a.norm_eps) : 1.0f;
+  T* dst = is_q ? static_cast<T*>(a.q) + static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(h) * a.dim
+                : static_cast<T*>(a.kc) + static_cast<int64_t>(slot) * a.k_row + static_cast<int64_t>(h) * a.dim;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < nv) store4(dst + 4 * c, make_float4(v[k].x * r, v[k].y * r, v[k].z * r, v[k].w * r));
+  }
+}
+
 struct AttnArgs {
   void* out; int64_t ldo;
   const void* q; int64_t ldq;
@@ -539,6 +588,15 @@ extern "C" int nvllm_attn_rope_norm_store(void* q, int64_t ldq, void* k_cache, v
                         reinterpret_cast<const float2*>(rope_table), rot_dims, max_pos, norm_eps, slots, n, heads, kv_heads, dim, vdim, v_from_k};
   const int64_t items = static_cast<int64_t>(n) * (heads + kv_heads + (v_from_k ? 0 : kv_heads));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // values from keys, heads of 4..512 values in 16-byte steps, aligned rows: the one-pass kernel
+  if (v_from_k && dim % 4 == 0 && dim <= 512 && ldp % 4 == 0 && ldq % 4 == 0 && k_row % 4 == 0 && v_row % 4 == 0 && aligned16(proj) && aligned16(q) &&
+      aligned16(k_cache) && aligned16(v_cache) && aligned16(q_bias) && aligned16(k_bias)) {
+    const int64_t vitems = static_cast<int64_t>(n) * (heads + kv_heads);
+    if (dtype == NVLLM_BF16) attn_rope_norm_store_vec_kernel<bf16><<<static_cast<unsigned>((vitems + 3) / 4), 128, 0, st>>>(a);
+    else attn_rope_norm_store_vec_kernel<float><<<static_cast<unsigned>((vitems + 3) / 4), 128, 0, st>>>(a);
+    NVLLM_LAUNCH_CHECK("attn_rope_norm_store_vec_kernel");
+    return 0;
+  }
   if (dtype == NVLLM_BF16) attn_rope_norm_store_kernel<bf16><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);
   else attn_rope_norm_store_kernel<float><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);
   NVLLM_LAUNCH_CHECK("attn_rope_norm_store_kernel");

@@ -98,12 +98,13 @@ def test_rms_norm_rows_into_cache_slots(cuda, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_embedding_bigram_across_portions_and_slots(cuda, dtype):
+@pytest.mark.parametrize("hid", [10, 16])
+def test_embedding_bigram_across_portions_and_slots(cuda, dtype, hid):
     """Three sequences in portions; the token before a portion comes from the state slot, the first token of a sequence reads
     the extra row although its slot still holds another sequence's last token."""
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(5)
-    vocab, hid, buckets, mp, mc, scale = 29, 10, 17, 13, 5, 2.5
+    vocab, buckets, mp, mc, scale = 29, 17, 13, 5, 2.5
     bg = {"buckets": buckets, "mul_prev": mp, "mul_cur": mc}
     table, bigram = Z.bf16_round(rng.standard_normal((vocab, hid))), Z.bf16_round(rng.standard_normal((buckets + 1, hid)))
     seqs = [rng.integers(0, vocab, n).tolist() for n in (9, 1, 6)]
@@ -143,12 +144,14 @@ def _paged(rng, ctxs, bs, spare=3):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,rot,v_from_k", [(4, 2, 8, 4, True), (3, 3, 10, 10, True), (2, 1, 6, 0, False), (1, 1, 16, 6, False)])
+@pytest.mark.parametrize("H,G,D,rot,v_from_k", [(4, 2, 8, 4, True), (3, 3, 10, 10, True), (2, 1, 6, 0, False), (1, 1, 16, 6, False), (5, 5, 12, 6, True),
+                                                 (2, 1, 128, 64, True), (3, 1, 132, 132, True), (2, 2, 16, 0, True)])
 def test_attn_rope_norm_store(cuda, dtype, H, G, D, rot, v_from_k):
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(H * 100 + D)
     n, eps, base, V = 7, 1e-3, 50.0, (D if v_from_k else 5)
-    cols = H * D + G * D + (0 if v_from_k else G * V) + 3
+    cols = H * D + G * D + (0 if v_from_k else G * V)
+    cols += 4 if cols % 4 == 0 else 3            # rows of 16-byte multiples take the one-pass kernel
     proj = rng.standard_normal((n, cols))
     qb, kb = rng.standard_normal(H * D), rng.standard_normal(G * D)
     vb = None if v_from_k else rng.standard_normal(G * V)
