@@ -353,7 +353,8 @@ int nvllm_linear(void* y, const void* x, const void* w, int32_t m, int32_t n, in
  * (w + group * group_stride_w; < 0: tile unused).  row_src (nullable): row r reads x[row_src[r]] (< 0: padding row, not
  * written).  glu == 1: every group's weights are [gate rows (n) | up rows (n)] x k and the output is
  * min(g, limit) * sigmoid(1.702 * min(g, limit)) * (clamp(u, -limit, limit) + 1), g and u rounded to the operand type first;
- * glu == 2: the output is relu(v)^2 of the plain product v (rounded to the operand type first). */
+ * glu == 2: the output is relu(v)^2 of the plain product v (rounded to the operand type first);
+ * glu == 3: as glu == 1 with the plain gate, silu(g) * u. */
 int nvllm_linear_grouped(void* y, const void* x, const void* w, int32_t max_rows, int32_t n, int32_t k, int64_t ldx,
                          int64_t ldw, int64_t ldy, int64_t group_stride_w, const int32_t* row_src,
                          const int32_t* tile_group, int32_t glu, float limit, int32_t dtype, int32_t out_dtype,
@@ -554,6 +555,48 @@ int nvllm_gated_delta_recurrence(float* y, int64_t ldy, const float* q, int64_t 
 int nvllm_gated_group_norm_act(void* out, int64_t ldo, const float* y, int64_t ldy, const float* gate, int64_t ldg, const float* w,
                                int32_t w_shared, int32_t n, int32_t cols, int32_t parts, float eps, int32_t gate_first,
                                int32_t gate_act, int32_t out_dtype, void* stream);
+
+/* ---- Post-norm blocks, chunked attention with a distance bias, rotated values, xIELU, routing on logits -------------- */
+
+/* Attention preparation for layers whose queries and keys are RMS-normed over the whole projection (all heads at once).
+ * proj: f32 [n, >= q_cols + k_cols + v_cols] rows [q | k | v | ...]; q = rms(q) * q_norm_w in `dtype`; k = rms(k) * k_norm_w and
+ * v into cache rows slots[i] (slot < 0: nothing stored).  Weights f32, nullable (1).  k_cols == 0 (then v_cols == 0): the
+ * layer reads another layer's keys and values and only its queries are prepared. */
+int nvllm_attn_wide_norm_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row, const float* proj,
+                               int64_t ldp, const float* q_norm_w, const float* k_norm_w, float eps, const int32_t* slots,
+                               int32_t n, int32_t q_cols, int32_t k_cols, int32_t v_cols, int32_t dtype, void* stream);
+/* nvllm_attn_rope_norm_store with the pairing of the rotation as a parameter (halves == 0: neighbours (2i, 2i+1); != 0: value
+ * i with i + rot_dims / 2) and, with v_rope_table (as nvllm_rope_table_interleaved builds for dims = vdim; nullable), the value
+ * heads rotated by their position over all of vdim in the same pairing before they are stored. */
+int nvllm_attn_rotary_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row, const float* proj,
+                            int64_t ldp, const float* q_bias, const float* k_bias, const float* v_bias, const int64_t* positions,
+                            const float* rope_table, int32_t rot_dims, int32_t halves, const float* v_rope_table, int32_t max_pos,
+                            float norm_eps, const int32_t* slots, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
+                            int32_t vdim, int32_t v_from_k, int32_t dtype, void* stream);
+/* nvllm_window_attention with four more options, each off when zero / NULL:
+ *   chunk > 0: position p sees only the keys of its own chunk, floor(p / chunk) * chunk .. p (chunks count from position 0);
+ *   head_scale (f32 [heads]): the scaled score of head h is multiplied by head_scale[h];
+ *   dist_bias (f32 [dist_rows, heads]): dist_bias[min(p - j, dist_rows - 1), h] is added to the score of key j (after scale,
+ *     temperature and cap; the sink gets none);
+ *   out_rot_table (f32 [max_pos, vdim / 2, 2] of (cos, sin), as nvllm_rope_table_interleaved builds for dims = vdim): every
+ *     head's output is turned by -p, value m paired with m + vdim / 2, before the gate (values that were stored rotated by
+ *     their own position thus enter the sum by their distance). */
+int nvllm_biased_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
+                           int32_t gate_per_head, const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
+                           const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables, int32_t table_cap,
+                           int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, float scale,
+                           float softcap, float temp_coef, int32_t temp_every, int32_t window, const float* sinks, int32_t chunk,
+                           const float* head_scale, const float* dist_bias, int32_t dist_rows, const float* out_rot_table,
+                           int32_t max_pos, const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream);
+/* nvllm_ff_activation with parameters.  kind 2 (in: [n, ff]): xIELU with the two learned numbers params[0..1] (device, f32):
+ *   z > 0: softplus(p0) z^2 + z / 2;   z <= 0: (1/2 + softplus(p1)) (exp(z) - 1 - z) + z / 2.   kinds 0 / 1 ignore params. */
+int nvllm_ff_activation_params(void* out, const void* in, int32_t n, int32_t ff, int32_t kind, const float* params, int32_t dtype,
+                               void* stream);
+/* Routing on the logits: z = logits + bias (bias nullable); chosen = the `top` largest z (ties: lowest index);
+ * topk_w = softmax over the chosen z alone.  logits: f32 [n, experts] with rows ld apart, experts <= 3072.
+ * (nvllm_linear_grouped with glu == 3 is the expert product with the plain gate silu(g) * u.) */
+int nvllm_moe_route_logits(int32_t* topk_idx, float* topk_w, const float* logits, int64_t ld, const float* bias, int32_t n,
+                           int32_t experts, int32_t top, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Engine-level C ABI: the C++ host runtime that mirrors the reference's Rust types one-to-one

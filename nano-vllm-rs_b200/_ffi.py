@@ -112,6 +112,13 @@ PROTOTYPES = {
                                          i32, i32, i32, vp]),
     "nvllm_window_attention": (i32, [vp, i64, vp, i64, vp, i64, i32, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                      f32, f32, f32, i32, i32, vp, vp, i32, i32, vp]),
+    "nvllm_attn_wide_norm_store": (i32, [vp, i64, vp, vp, i64, i64, vp, i64, vp, vp, f32, vp, i32, i32, i32, i32, i32, vp]),
+    "nvllm_attn_rotary_store": (i32, [vp, i64, vp, vp, i64, i64, vp, i64, vp, vp, vp, vp, vp, i32, i32, vp, i32, f32, vp, i32, i32, i32,
+                                      i32, i32, i32, i32, vp]),
+    "nvllm_biased_attention": (i32, [vp, i64, vp, i64, vp, i64, i32, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                     f32, f32, f32, i32, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, vp]),
+    "nvllm_ff_activation_params": (i32, [vp, vp, i32, i32, i32, vp, i32, vp]),
+    "nvllm_moe_route_logits": (i32, [vp, vp, vp, i64, vp, i32, i32, i32, vp]),
     "nvllm_latent_window_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp, i64, i32, i32, i32, i32, i32, f32, i32,
                                             vp, vp, i64, vp, sz, i32, vp]),
     "nvllm_delta_prepare": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, i32, i32, i32, i32, f32, f32, vp]),

@@ -40,6 +40,36 @@ __global__ void attn_bias_store_kernel(T* __restrict__ q, int64_t ldq, T* __rest
   for (int c = threadIdx.x; c < vn; c += blockDim.x) stv(vc + slot * v_row + c, p[qn + kn + c] + (vb ? vb[c] : 0.f));
 }
 
+// The same step for layers whose queries and keys are RMS-normed over the WHOLE projection (all heads of a token at once,
+// one weight per column): q = rms(proj_q) * qw in the operand type, k = rms(proj_k) * kw and v into their cache rows.
+// kn == 0: the layer has no keys / values of its own (it reads another layer's cache).  CTA per token; statistics f32.
+template <typename T>
+__global__ void __launch_bounds__(256) attn_wide_norm_store_kernel(T* __restrict__ q, int64_t ldq, T* __restrict__ kc, T* __restrict__ vc,
+                                                                   int64_t k_row, int64_t v_row, const float* __restrict__ proj, int64_t ldp,
+                                                                   const float* __restrict__ qw, const float* __restrict__ kw,
+                                                                   const int32_t* __restrict__ slots, int qn, int kn, int vn, float eps) {
+  __shared__ float red[2][8];
+  const int64_t t = blockIdx.x;
+  const float* p = proj + t * ldp;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < qn; c += 256) sq = fmaf(p[c], p[c], sq);
+  for (int c = threadIdx.x; c < kn; c += 256) sk = fmaf(p[qn + c], p[qn + c], sk);
+  sq = warp_sum(sq); sk = warp_sum(sk);
+  if (lane == 0) { red[0][wid] = sq; red[1][wid] = sk; }
+  __syncthreads();
+  sq = sk = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { sq += red[0][i]; sk += red[1][i]; }   // fixed order: every thread holds the same sums
+  const float rq = 1.0f / sqrtf(sq / qn + eps);
+  for (int c = threadIdx.x; c < qn; c += 256) stv(q + t * ldq + c, p[c] * rq * (qw ? qw[c] : 1.0f));
+  const int32_t slot = slots[t];
+  if (slot < 0 || kn == 0) return;
+  const float rk = 1.0f / sqrtf(sk / kn + eps);
+  for (int c = threadIdx.x; c < kn; c += 256) stv(kc + slot * k_row + c, p[qn + c] * rk * (kw ? kw[c] : 1.0f));
+  for (int c = threadIdx.x; c < vn; c += 256) stv(vc + slot * v_row + c, p[qn + kn + c]);
+}
+
 struct RopeStoreArgs {
   void* q; int64_t ldq;
   void *kc, *vc; int64_t k_row, v_row;
@@ -49,6 +79,8 @@ struct RopeStoreArgs {
   float norm_eps;
   const int32_t* slots;
   int n, heads, kv_heads, dim, vdim, v_from_k;
+  int halves;            // pairing of the rotation: 0 = neighbours (2i, 2i + 1); 1 = halves (i, i + rot_dims / 2)
+  const float2* vtable;  // non-null: every value head is rotated too, over all of vdim (same pairing), by this table
 };
 
 // One warp per (token, head) over the heads [q heads | key heads | value heads].  A query or key head: bias, rotation of the
@@ -69,7 +101,27 @@ __global__ void __launch_bounds__(128) attn_rope_norm_store_kernel(const RopeSto
     if (slot < 0) return;
     const int g = hh - a.heads - a.kv_heads;
     T* dst = static_cast<T*>(a.vc) + static_cast<int64_t>(slot) * a.v_row + static_cast<int64_t>(g) * a.vdim;
-    for (int c = lane; c < a.vdim; c += 32) stv(dst + c, p[qn + kn + g * a.vdim + c] + (a.vb ? a.vb[g * a.vdim + c] : 0.f));
+    const float* vs = p + qn + kn + g * a.vdim;
+    const float* vbias = a.vb ? a.vb + g * a.vdim : nullptr;
+    if (a.vtable == nullptr) {
+      for (int c = lane; c < a.vdim; c += 32) stv(dst + c, vs[c] + (vbias ? vbias[c] : 0.f));
+      return;
+    }
+    int64_t vp = a.positions[t];
+    vp = vp < 0 ? 0 : (vp >= a.max_pos ? a.max_pos - 1 : vp);
+    const int hv = a.vdim / 2;
+    const float2* vt = a.vtable + vp * hv;
+    for (int c = lane; c < a.vdim; c += 32) {
+      float v = vs[c] + (vbias ? vbias[c] : 0.f);
+      if (c < 2 * hv) {
+        const int pc = a.halves ? (c < hv ? c + hv : c - hv) : (c ^ 1);
+        const bool second = a.halves ? c >= hv : (c & 1);
+        const float o = vs[pc] + (vbias ? vbias[pc] : 0.f);
+        const float2 cs = vt[a.halves ? (c < hv ? c : c - hv) : (c >> 1)];
+        v = second ? fmaf(v, cs.x, o * cs.y) : fmaf(v, cs.x, -o * cs.y);
+      }
+      stv(dst + c, v);
+    }
     return;
   }
   const bool is_q = hh < a.heads;
@@ -91,9 +143,12 @@ __global__ void __launch_bounds__(128) attn_rope_norm_store_kernel(const RopeSto
   auto value = [&](int c) {
     float v = src[c] + (bias ? bias[c] : 0.f);
     if (c < a.rot_dims) {
-      const float o = src[c ^ 1] + (bias ? bias[c ^ 1] : 0.f);
-      const float2 cs = tab[c >> 1];
-      v = (c & 1) ? fmaf(v, cs.x, o * cs.y) : fmaf(v, cs.x, -o * cs.y);   // (u cos - v sin, v cos + u sin)
+      const int hr = a.rot_dims / 2;
+      const int pc = a.halves ? (c < hr ? c + hr : c - hr) : (c ^ 1);
+      const bool second = a.halves ? c >= hr : (c & 1);
+      const float o = src[pc] + (bias ? bias[pc] : 0.f);
+      const float2 cs = tab[a.halves ? (c < hr ? c : c - hr) : (c >> 1)];
+      v = second ? fmaf(v, cs.x, o * cs.y) : fmaf(v, cs.x, -o * cs.y);   // (u cos - v sin, v cos + u sin)
     }
     return v;
   };
@@ -165,7 +220,21 @@ struct AttnArgs {
   float scale, softcap, temp_coef; int temp_every;
   int window; const float* sinks; int gate_per_head;
   const int32_t* dense_cu;   // non-null (and tables null): keys are not paged, key j of sequence s is row dense_cu[s] + j
+  // positional options of nvllm_biased_attention (all off when zero / null)
+  int chunk;                 // > 0: position p sees only the keys of its own chunk, floor(p / chunk) * chunk .. p
+  const float* head_scale;   // [heads]: a factor per head on the scaled score
+  const float* dist_bias;    // [dist_rows, heads]: added to the score of key j: dist_bias[min(p - j, dist_rows - 1), h]
+  int dist_rows;
+  const float2* out_rot;     // [max_pos, vdim / 2] (cos, sin): every head's output is turned by -p, value m paired with m + vdim / 2
+  int max_pos;
 };
+
+// first key a row at position p sees
+__device__ __forceinline__ int first_key(const AttnArgs& a, int p) {
+  int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, p / a.chunk * a.chunk);
+  return lo;
+}
 
 constexpr int kMaxVPerLane = 16;  // vdim <= 512
 
@@ -173,16 +242,16 @@ constexpr int kMaxVPerLane = 16;  // vdim <= 512
 // the online-softmax statistics, then every lane accumulates its output dimensions over the 32 keys.
 template <typename T>
 __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a) {
-  extern __shared__ float qs[];  // [4 warps][dim]
+  extern __shared__ float qs[];  // [4 warps][max(dim, vdim)]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   if (item >= static_cast<int64_t>(a.n) * a.heads) return;
   const int t = static_cast<int>(item / a.heads), h = static_cast<int>(item % a.heads);
   const int g = h / (a.heads / a.kv_heads);
-  float* qw = qs + warp * a.dim;
+  float* qw = qs + warp * max(a.dim, a.vdim);
   const int64_t pos = a.positions[t];
   const float temp = 1.0f + a.temp_coef * logf(floorf(static_cast<float>((pos + 1) / a.temp_every)) + 1.0f);
-  const float qscale = a.scale * temp;
+  const float qscale = a.scale * temp * (a.head_scale ? a.head_scale[h] : 1.0f);
   const T* q = static_cast<const T*>(a.q) + t * a.ldq + static_cast<int64_t>(h) * a.dim;
   for (int c = lane; c < a.dim; c += 32) qw[c] = ldv(q + c) * qscale;
   __syncwarp();
@@ -194,7 +263,7 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
 #pragma unroll
   for (int i = 0; i < kMaxVPerLane; ++i) acc[i] = 0.f;
   const int nkeys = static_cast<int>(pos) + 1;
-  const int first = a.window > 0 ? max(0, nkeys - a.window) : 0;   // passes start at multiples of 32 whatever the window
+  const int first = first_key(a, static_cast<int>(pos));   // passes start at multiples of 32 whatever the window or chunk
   for (int j0 = first & ~31; j0 < nkeys; j0 += 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
@@ -207,6 +276,7 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
         float d = 0.f;
         for (int c = 0; c < a.dim; ++c) d = fmaf(qw[c], ldv(kr + c), d);
         s = a.softcap > 0.f ? a.softcap * tanhf(d / a.softcap) : d;
+        if (a.dist_bias) s += a.dist_bias[static_cast<int64_t>(min(nkeys - 1 - j, a.dist_rows - 1)) * a.heads + h];
       }
     }
     const float mt = warp_max(s);
@@ -240,11 +310,33 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   T* o = static_cast<T*>(a.out) + t * a.ldo + static_cast<int64_t>(h) * a.vdim;
   const float* gt = a.gate ? a.gate + t * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim) : nullptr;
+  if (a.out_rot) {   // the head's output turned by -pos: the pairs span lanes, so the row passes through shared memory
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < kMaxVPerLane; ++i) {
+      const int c = lane + 32 * i;
+      if (c < a.vdim) qw[c] = acc[i] * inv;
+    }
+    __syncwarp();
+    const int hf = a.vdim / 2;
+    const float2* tab = a.out_rot + (pos < 0 ? 0 : (pos >= a.max_pos ? a.max_pos - 1 : pos)) * hf;
+#pragma unroll
+    for (int i = 0; i < kMaxVPerLane; ++i) {
+      const int c = lane + 32 * i;
+      if (c < 2 * hf) {
+        const float2 cs = tab[c < hf ? c : c - hf];
+        acc[i] = c < hf ? fmaf(qw[c], cs.x, qw[c + hf] * cs.y) : fmaf(qw[c], cs.x, -qw[c - hf] * cs.y);   // (u cos + v sin, v cos - u sin)
+      } else if (c < a.vdim) {
+        acc[i] = qw[c];
+      }
+    }
+  }
+  const float inv_o = a.out_rot ? 1.0f : inv;
 #pragma unroll
   for (int i = 0; i < kMaxVPerLane; ++i) {
     const int c = lane + 32 * i;
     if (c < a.vdim) {
-      float v = acc[i] * inv;
+      float v = acc[i] * inv_o;
       if (gt) v *= 1.0f / (1.0f + expf(-gt[a.gate_per_head ? 0 : c]));
       stv(o + c, v);
     }
@@ -271,10 +363,12 @@ __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2
 
 // One warp's share of a key tile: 16 rows x (16 NP) keys -> S on tensor cores, cap / mask / online softmax in f32, then
 // O[:, 0 .. 16 VP) += P . V.  k_addr / v_addr are the warp's ldmatrix lane addresses of its first key (and first value column).
-template <int DMAX, int VMAX, int NP, int VP, int QS, int VS>
+// bias (EXT): per row, the column of the distance-bias table of the row's head (null: none), rows `heads` apart.
+template <int DMAX, int VMAX, int NP, int VP, int QS, int VS, bool EXT>
 __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2], float (&l)[2], uint32_t q_addr, uint32_t k_addr,
-                                          uint32_t v_addr, int key0, const int (&pos)[2], int back, const float (&qscale)[2],
-                                          bool capped, float cap2, bool need_mask, int tq4) {
+                                          uint32_t v_addr, int key0, const int (&pos)[2], const int (&lo)[2], const float (&qscale)[2],
+                                          bool capped, float cap2, bool need_mask, int tq4, const float* const (&bias)[2], int heads,
+                                          int dist_rows) {
   float s[2 * NP][4];
 #pragma unroll
   for (int i = 0; i < 2 * NP; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -298,7 +392,8 @@ __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2]
       const int i = e >> 1, j = key0 + nt * 8 + 2 * tq4 + (e & 1);
       float v = s[nt][e] * qscale[i];            // with a cap: the score over the cap; without: the score in log2 units
       if (capped) v = cap2 * fast_tanh(v);
-      if (need_mask) v = (j <= pos[i] && j >= pos[i] - back) ? v : -INFINITY;   // back: window - 1, or no bound
+      if (EXT) { if (bias[i] != nullptr && j <= pos[i]) v = fmaf(__ldg(bias[i] + min(pos[i] - j, dist_rows - 1) * heads), kLog2e, v); }
+      if (need_mask) v = (j <= pos[i] && j >= lo[i]) ? v : -INFINITY;   // lo: the first key of the row's window or chunk
       s[nt][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -341,7 +436,7 @@ __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2]
   }
 }
 
-template <int DMAX, int VMAX>
+template <int DMAX, int VMAX, bool EXT>
 __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const AttnArgs a, const int32_t* __restrict__ cu_tokens, int n_seqs, int tq,
                                                               int group) {
   constexpr int QS = DMAX + 8, VS = VMAX + 8;       // shared-memory row strides (elements): 16-byte rows, conflict-free ldmatrix
@@ -408,20 +503,26 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   // Otherwise warp w owns rows [16 w, +16) and walks whole tiles (warps without rows only help with the copies).
   const bool few = ntok * group <= 16;
   const int rbase = few ? 0 : warp * 16, kq = warp & 3, vh = warp >> 2;
-  int pos[2]; float qscale[2]; bool valid[2];
-  const int back = a.window > 0 ? a.window - 1 : (1 << 30);   // a row sees the keys pos - back .. pos
+  int pos[2], lo[2]; float qscale[2]; bool valid[2];
+  const float* bias[2] = {nullptr, nullptr};
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = rbase + gq + 8 * i, t = r / group;
     valid[i] = t < ntok && r < tq * group;
     pos[i] = valid[i] ? static_cast<int>(a.positions[tok0 + t]) : -1;
+    lo[i] = valid[i] ? first_key(a, pos[i]) : -(1 << 30);   // a row sees the keys lo .. pos
     qscale[i] = a.scale * (1.0f + a.temp_coef * logf(floorf(static_cast<float>((pos[i] + 1) / a.temp_every)) + 1.0f)) *
                 (a.softcap > 0.f ? 1.0f / a.softcap : kLog2e);
+    if (EXT) {
+      const int h = g * group + r % group;
+      if (a.head_scale) qscale[i] *= a.head_scale[h];
+      if (a.dist_bias) bias[i] = a.dist_bias + h;
+    }
   }
   // the smallest position of the warp's rows decides whether a tile needs the causal mask (empty rows count as hidden)
   const bool warp_has_rows = rbase / group < ntok;
   const int min_pos = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));
-  const int max_lo = __reduce_max_sync(0xffffffffu, max(pos[0], pos[1])) - back;   // a tile that starts before it needs the window's mask
+  const int max_lo = __reduce_max_sync(0xffffffffu, max(lo[0], lo[1]));   // a tile that starts before it needs the window's / chunk's mask
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[VMAX / 8][4];
 #pragma unroll
@@ -431,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   const int ntiles = (nkeys + kKeys - 1) / kKeys;
   // with a window the first tile is the one that holds the first key the CTA's first token sees (tiles stay anchored at
   // multiples of 64 from the sequence's start)
-  const int kt0 = a.window > 0 ? max(0, static_cast<int>(a.positions[tok0]) - a.window + 1) / kKeys : 0;
+  const int kt0 = first_key(a, static_cast<int>(a.positions[tok0])) / kKeys;   // (windows and chunks only move forward with the position)
   if (tid < kKeys) { slot_s[kt0 & 1][tid] = lookup(kt0); slot_s[(kt0 + 1) & 1][tid] = lookup(kt0 + 1); }
   __syncthreads();
   load_tile(kt0, kt0 & 1);
@@ -448,16 +549,17 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     if (few) {
       const int key0 = kt * kKeys + kq * 16;
       if (key0 < nkeys)
-        attn_tile<DMAX, VMAX, 1, VMAX / 32, QS, VS>(o, m, l, q_addr, smem_u32(kb + kq * 16 * QS + k_lane),
-                                                    smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, back, qscale, capped, cap2,
-                                                    key0 + 15 > min_pos || key0 < max_lo, tq4);
+        attn_tile<DMAX, VMAX, 1, VMAX / 32, QS, VS, EXT>(o, m, l, q_addr, smem_u32(kb + kq * 16 * QS + k_lane),
+                                                         smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, lo, qscale, capped, cap2,
+                                                         key0 + 15 > min_pos || key0 < max_lo, tq4, bias, a.heads, a.dist_rows);
     } else if (warp_has_rows) {
       // two halves of 32 keys: half the score registers of a 64-key pass (no spills under the 128-register cap)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf)
-        attn_tile<DMAX, VMAX, 2, VMAX / 16, QS, VS>(o, m, l, q_addr, smem_u32(kb + hf * 32 * QS + k_lane), smem_u32(vb + hf * 32 * VS + v_lane),
-                                                    kt * kKeys + hf * 32, pos, back, qscale, capped, cap2,
-                                                    kt * kKeys + hf * 32 + 31 > min_pos || kt * kKeys + hf * 32 < max_lo, tq4);
+        attn_tile<DMAX, VMAX, 2, VMAX / 16, QS, VS, EXT>(o, m, l, q_addr, smem_u32(kb + hf * 32 * QS + k_lane), smem_u32(vb + hf * 32 * VS + v_lane),
+                                                         kt * kKeys + hf * 32, pos, lo, qscale, capped, cap2,
+                                                         kt * kKeys + hf * 32 + 31 > min_pos || kt * kKeys + hf * 32 < max_lo, tq4, bias, a.heads,
+                                                         a.dist_rows);
     }
     if (tid < kKeys) slot_s[kt & 1][tid] = slot_ahead;   // tile kt's slots were consumed by load_tile(kt) an iteration ago
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it
@@ -485,10 +587,13 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     }
     __syncthreads();
     const int rows = ntok * group;
-    for (int e = tid; e < rows * a.vdim; e += kThreads) {
-      const int r = e / a.vdim, c = e - r * a.vdim, t = r / group, h = g * group + r % group;
+    // with the output rotation a thread merges both values of a pair (c, c + vdim / 2), turns them and stores them
+    const bool rot = EXT && a.out_rot != nullptr;
+    const int cols = rot ? a.vdim / 2 : a.vdim;
+    for (int e = tid; e < rows * cols; e += kThreads) {
+      const int r = e / cols, c = e - r * cols, t = r / group, h = g * group + r % group;
       float mm = fmaxf(fmaxf(ms[r], ms[16 + r]), fmaxf(ms[32 + r], ms[48 + r]));
-      float num = 0.f, den = 0.f;
+      float num = 0.f, num2 = 0.f, den = 0.f;
       if (a.sinks) {   // the sink joins the denominator only (scores are in log2 units here)
         const float sk = a.sinks[h] * kLog2e;
         mm = fmaxf(mm, sk);
@@ -498,11 +603,24 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
       for (int k = 0; k < 4; ++k) {
         const float w = fast_exp2(ms[k * 16 + r] - mm);     // a quarter that saw no key: exp2(-inf) = 0
         num = fmaf(w, os[(k * 16 + r) * VMAX + c], num);
+        if (rot) num2 = fmaf(w, os[(k * 16 + r) * VMAX + c + cols], num2);
         den = fmaf(w, ls[k * 16 + r], den);
       }
       float v = den > 0.f ? num / den : 0.f;
-      if (a.gate) v *= 1.0f / (1.0f + __expf(-a.gate[static_cast<int64_t>(tok0 + t) * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim + c)]));
-      static_cast<bf16*>(a.out)[static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim + c] = __float2bfloat16_rn(v);
+      bf16* op = static_cast<bf16*>(a.out) + static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim;
+      const float* gt = a.gate ? a.gate + static_cast<int64_t>(tok0 + t) * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim) : nullptr;
+      if (rot) {
+        float v2 = den > 0.f ? num2 / den : 0.f;
+        const int p = static_cast<int>(a.positions[tok0 + t]);
+        const float2 cs = a.out_rot[static_cast<int64_t>(p < 0 ? 0 : (p >= a.max_pos ? a.max_pos - 1 : p)) * cols + c];
+        const float u = v;
+        v = fmaf(u, cs.x, v2 * cs.y);                      // turned by -position: (u cos + v sin, v cos - u sin)
+        v2 = fmaf(v2, cs.x, -u * cs.y);
+        if (gt) v2 *= 1.0f / (1.0f + __expf(-gt[a.gate_per_head ? 0 : c + cols]));
+        op[c + cols] = __float2bfloat16_rn(v2);
+      }
+      if (gt) v *= 1.0f / (1.0f + __expf(-gt[a.gate_per_head ? 0 : c]));
+      op[c] = __float2bfloat16_rn(v);
     }
     return;
   }
@@ -520,6 +638,17 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     bf16* op = static_cast<bf16*>(a.out) + static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim;
     const float* gt = a.gate ? a.gate + static_cast<int64_t>(tok0 + t) * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim) : nullptr;
     const float gh = (gt && a.gate_per_head) ? 1.0f / (1.0f + __expf(-gt[0])) : 1.0f;
+    if (EXT && a.out_rot != nullptr) {   // vdim == VMAX here: a thread's columns c and c + VMAX / 2 are both its own
+      const int p = pos[i] >= a.max_pos ? a.max_pos - 1 : pos[i];
+      const float4* tab = reinterpret_cast<const float4*>(a.out_rot + static_cast<int64_t>(p) * (VMAX / 2));
+#pragma unroll
+      for (int vt = 0; vt < VMAX / 16; ++vt) {
+        const float4 cs = __ldg(tab + vt * 4 + tq4);     // (cos, sin) of the pairs c and c + 1, c = vt * 8 + 2 tq4
+        const float u0 = o[vt][2 * i], w0 = o[vt + VMAX / 16][2 * i], u1 = o[vt][2 * i + 1], w1 = o[vt + VMAX / 16][2 * i + 1];
+        o[vt][2 * i] = fmaf(u0, cs.x, w0 * cs.y);            o[vt + VMAX / 16][2 * i] = fmaf(w0, cs.x, -u0 * cs.y);
+        o[vt][2 * i + 1] = fmaf(u1, cs.z, w1 * cs.w);        o[vt + VMAX / 16][2 * i + 1] = fmaf(w1, cs.z, -u1 * cs.w);
+      }
+    }
 #pragma unroll
     for (int vt = 0; vt < VMAX / 8; ++vt) {
       const int c = vt * 8 + 2 * tq4;
@@ -531,13 +660,13 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   }
 }
 
-template <int DMAX, int VMAX>
+template <int DMAX, int VMAX, bool EXT>
 int launch_mma(const AttnArgs& a, const int32_t* cu_tokens, int n_seqs, cudaStream_t st) {
   const int group = a.heads / a.kv_heads, tq = kRows / group;
   const size_t smem = (static_cast<size_t>(kRows) * (DMAX + 8) + 2 * kKeys * (DMAX + 8) + 2 * kKeys * (VMAX + 8)) * sizeof(bf16);
-  NVLLM_SMEM_ATTR_ONCE((capped_attn_mma_kernel<DMAX, VMAX>), smem);
+  NVLLM_SMEM_ATTR_ONCE((capped_attn_mma_kernel<DMAX, VMAX, EXT>), smem);
   dim3 grid((a.n + tq - 1) / tq + n_seqs, a.kv_heads);
-  capped_attn_mma_kernel<DMAX, VMAX><<<grid, kThreads, smem, st>>>(a, cu_tokens, n_seqs, tq, group);
+  capped_attn_mma_kernel<DMAX, VMAX, EXT><<<grid, kThreads, smem, st>>>(a, cu_tokens, n_seqs, tq, group);
   NVLLM_LAUNCH_CHECK("capped_attn_mma_kernel");
   return 0;
 }
@@ -567,11 +696,42 @@ extern "C" int nvllm_attn_bias_store(void* q, int64_t ldq, void* k_cache, void* 
   return 0;
 }
 
+extern "C" int nvllm_attn_wide_norm_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row,
+                                          const float* proj, int64_t ldp, const float* q_norm_w, const float* k_norm_w, float eps,
+                                          const int32_t* slots, int32_t n, int32_t q_cols, int32_t k_cols, int32_t v_cols, int32_t dtype,
+                                          void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && q_cols > 0 && k_cols >= 0 && v_cols >= 0 && (k_cols > 0 || v_cols == 0) && ldq >= q_cols && ldp >= q_cols + k_cols + v_cols &&
+                      (k_cols == 0 || (k_row >= k_cols && v_row >= v_cols)), NVLLM_ERR_ARG, "attn_wide_norm_store: sizes");
+  NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "attn_wide_norm_store: dtype %d", dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(q && proj && slots && (k_cols == 0 || (k_cache && v_cache)), NVLLM_ERR_ARG, "attn_wide_norm_store: NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == NVLLM_BF16)
+    attn_wide_norm_store_kernel<bf16><<<n, 256, 0, st>>>(static_cast<bf16*>(q), ldq, static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache),
+                                                         k_row, v_row, proj, ldp, q_norm_w, k_norm_w, slots, q_cols, k_cols, v_cols, eps);
+  else
+    attn_wide_norm_store_kernel<float><<<n, 256, 0, st>>>(static_cast<float*>(q), ldq, static_cast<float*>(k_cache), static_cast<float*>(v_cache),
+                                                          k_row, v_row, proj, ldp, q_norm_w, k_norm_w, slots, q_cols, k_cols, v_cols, eps);
+  NVLLM_LAUNCH_CHECK("attn_wide_norm_store_kernel");
+  return 0;
+}
+
 extern "C" int nvllm_attn_rope_norm_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row,
                                           const float* proj, int64_t ldp, const float* q_bias, const float* k_bias,
                                           const float* v_bias, const int64_t* positions, const float* rope_table, int32_t rot_dims,
                                           int32_t max_pos, float norm_eps, const int32_t* slots, int32_t n, int32_t heads,
                                           int32_t kv_heads, int32_t dim, int32_t vdim, int32_t v_from_k, int32_t dtype, void* stream) {
+  return nvllm_attn_rotary_store(q, ldq, k_cache, v_cache, k_row, v_row, proj, ldp, q_bias, k_bias, v_bias, positions, rope_table, rot_dims, 0,
+                                 nullptr, max_pos, norm_eps, slots, n, heads, kv_heads, dim, vdim, v_from_k, dtype, stream);
+}
+
+extern "C" int nvllm_attn_rotary_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row,
+                                       const float* proj, int64_t ldp, const float* q_bias, const float* k_bias, const float* v_bias,
+                                       const int64_t* positions, const float* rope_table, int32_t rot_dims, int32_t halves,
+                                       const float* v_rope_table, int32_t max_pos, float norm_eps, const int32_t* slots, int32_t n,
+                                       int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t v_from_k, int32_t dtype,
+                                       void* stream) {
+  NVLLM_CHECK_ARG(v_rope_table == nullptr || !v_from_k, NVLLM_ERR_ARG, "attn_rotary_store: rotated values need a value projection of their own");
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim &&
                       max_pos > 0 && (!v_from_k || vdim == dim), NVLLM_ERR_ARG,
                   "attn_rope_norm_store: heads=%d/%d dim=%d vdim=%d rot_dims=%d (even, <= dim; values from keys need vdim == dim)", heads,
@@ -585,11 +745,12 @@ extern "C" int nvllm_attn_rope_norm_store(void* q, int64_t ldq, void* k_cache, v
   NVLLM_CHECK_ARG(q && k_cache && v_cache && proj && positions && slots && (rope_table || rot_dims == 0), NVLLM_ERR_ARG,
                   "attn_rope_norm_store: NULL");
   const RopeStoreArgs a{q, ldq, k_cache, v_cache, k_row, v_row, proj, ldp, q_bias, k_bias, v_bias, positions,
-                        reinterpret_cast<const float2*>(rope_table), rot_dims, max_pos, norm_eps, slots, n, heads, kv_heads, dim, vdim, v_from_k};
+                        reinterpret_cast<const float2*>(rope_table), rot_dims, max_pos, norm_eps, slots, n, heads, kv_heads, dim, vdim, v_from_k,
+                        halves != 0, reinterpret_cast<const float2*>(v_rope_table)};
   const int64_t items = static_cast<int64_t>(n) * (heads + kv_heads + (v_from_k ? 0 : kv_heads));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // values from keys, heads of 4..512 values in 16-byte steps, aligned rows: the one-pass kernel
-  if (v_from_k && dim % 4 == 0 && dim <= 512 && ldp % 4 == 0 && ldq % 4 == 0 && k_row % 4 == 0 && v_row % 4 == 0 && aligned16(proj) && aligned16(q) &&
+  if (v_from_k && !halves && dim % 4 == 0 && dim <= 512 && ldp % 4 == 0 && ldq % 4 == 0 && k_row % 4 == 0 && v_row % 4 == 0 && aligned16(proj) && aligned16(q) &&
       aligned16(k_cache) && aligned16(v_cache) && aligned16(q_bias) && aligned16(k_bias)) {
     const int64_t vitems = static_cast<int64_t>(n) * (heads + kv_heads);
     if (dtype == NVLLM_BF16) attn_rope_norm_store_vec_kernel<bf16><<<static_cast<unsigned>((vitems + 3) / 4), 128, 0, st>>>(a);
@@ -620,6 +781,22 @@ extern "C" int nvllm_window_attention(void* out, int64_t ldo, const void* q, int
                                       int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
                                       int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every, int32_t window,
                                       const float* sinks, const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream) {
+  return nvllm_biased_attention(out, ldo, q, ldq, gate, ldg, gate_per_head, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables,
+                                table_cap, block_size, n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window, sinks, 0,
+                                nullptr, nullptr, 0, nullptr, 0, cu_tokens, n_seqs, dtype, stream);
+}
+
+extern "C" int nvllm_biased_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
+                                      int32_t gate_per_head, const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
+                                      const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
+                                      int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
+                                      int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every, int32_t window,
+                                      const float* sinks, int32_t chunk, const float* head_scale, const float* dist_bias,
+                                      int32_t dist_rows, const float* out_rot_table, int32_t max_pos, const int32_t* cu_tokens,
+                                      int32_t n_seqs, int32_t dtype, void* stream) {
+  NVLLM_CHECK_ARG(chunk >= 0 && (dist_bias == nullptr || dist_rows > 0) && (out_rot_table == nullptr || (max_pos > 0 && vdim % 2 == 0)),
+                  NVLLM_ERR_ARG, "attention: chunk=%d dist_rows=%d max_pos=%d vdim=%d (an output rotation pairs the halves of an even vdim)", chunk,
+                  dist_rows, max_pos, vdim);
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && vdim <= 32 * kMaxVPerLane &&
                       dim <= 2048 && block_size > 0 && table_cap > 0 && temp_every > 0, NVLLM_ERR_ARG,
                   "attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 512)", n, heads, kv_heads, dim, vdim);
@@ -627,18 +804,31 @@ extern "C" int nvllm_window_attention(void* out, int64_t ldo, const void* q, int
   if (n == 0) return 0;
   NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && (block_tables || cu_tokens), NVLLM_ERR_ARG, "attention: NULL");
   AttnArgs a{out, ldo, q, ldq, gate, ldg, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables, table_cap, block_size,
-             n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window > 0 ? window : 0, sinks, gate_per_head, block_tables ? nullptr : cu_tokens};
+             n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window > 0 ? window : 0, sinks, gate_per_head, block_tables ? nullptr : cu_tokens,
+             chunk, head_scale, dist_bias, dist_rows, reinterpret_cast<const float2*>(out_rot_table), max_pos};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 with 16-byte rows and a token range per sequence: tensor cores; everything else (f32, odd sizes): one warp per row
   const int group = heads / kv_heads;
   if (dtype == NVLLM_BF16 && cu_tokens != nullptr && n_seqs > 0 && knobs().capped_mma && group <= kRows && dim % 8 == 0 && vdim % 8 == 0 &&
       dim <= 128 && vdim <= 128 && ldq % 8 == 0 && k_row % 8 == 0 && v_row % 8 == 0 && ldo % 2 == 0 && aligned16(q) && aligned16(k_cache) &&
       aligned16(v_cache) && (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
-    if (dim <= 64 && vdim <= 64) return launch_mma<64, 64>(a, cu_tokens, n_seqs, st);
-    return launch_mma<128, 128>(a, cu_tokens, n_seqs, st);
+    // the positional options live in a second instantiation, so that kernels without them keep their registers
+    const bool ext = head_scale != nullptr || dist_bias != nullptr || out_rot_table != nullptr;
+    const int vmax = vdim <= 64 ? 64 : 128;
+    // the output rotation pairs column c with c + vdim / 2 inside one thread's accumulators: vdim must fill the tile
+    if (out_rot_table == nullptr || (vdim == vmax && aligned16(out_rot_table))) {
+      if (!ext) {
+        if (dim <= 64 && vdim <= 64) return launch_mma<64, 64, false>(a, cu_tokens, n_seqs, st);
+        if (vdim <= 64) return launch_mma<128, 64, false>(a, cu_tokens, n_seqs, st);
+        return launch_mma<128, 128, false>(a, cu_tokens, n_seqs, st);
+      }
+      if (dim <= 64 && vdim <= 64) return launch_mma<64, 64, true>(a, cu_tokens, n_seqs, st);
+      if (vdim <= 64) return launch_mma<128, 64, true>(a, cu_tokens, n_seqs, st);
+      return launch_mma<128, 128, true>(a, cu_tokens, n_seqs, st);
+    }
   }
   const unsigned grid = static_cast<unsigned>((static_cast<int64_t>(n) * heads + 3) / 4);
-  const size_t smem = static_cast<size_t>(4) * dim * sizeof(float);
+  const size_t smem = static_cast<size_t>(4) * (dim > vdim ? dim : vdim) * sizeof(float);
   if (dtype == NVLLM_BF16) capped_attn_warp_kernel<bf16><<<grid, 128, smem, st>>>(a);
   else capped_attn_warp_kernel<float><<<grid, 128, smem, st>>>(a);
   NVLLM_LAUNCH_CHECK("capped_attn_warp_kernel");

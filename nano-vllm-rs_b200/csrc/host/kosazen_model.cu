@@ -508,10 +508,10 @@ ModelImpl* make_kosazen(const json::Value& cfg) {
 // ---- registry --------------------------------------------------------------------------------------------------
 namespace {
 struct Entry { const char* name; ModelImpl* (*make)(const json::Value&); };
-const Entry kRegistry[] = {{"Kosazen", make_kosazen}, {"Talapel", make_talapel}, {"Zudatar", make_zudatar}};
+const Entry kRegistry[] = {{"Kosazen", make_kosazen}, {"Talapel", make_talapel}, {"Zudatar", make_zudatar}, {"Zasorax", make_zasorax}};
 }  // namespace
 
-const char* registered_architectures() { return "Qwen3 (built in: qwen3-0.6b, qwen3-8b, qwen3-32b, ...), Kosazen, Talapel, Zudatar"; }
+const char* registered_architectures() { return "Qwen3 (built in: qwen3-0.6b, qwen3-8b, qwen3-32b, ...), Kosazen, Talapel, Zudatar, Zasorax"; }
 
 ModelImpl* make_model(const json::Value& cfg) {
   const std::string arch = cfg["architecture"].as_string();

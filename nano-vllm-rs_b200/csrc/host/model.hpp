@@ -71,5 +71,6 @@ const char* registered_architectures();
 ModelImpl* make_kosazen(const json::Value& cfg);  // kosazen_model.cu
 ModelImpl* make_talapel(const json::Value& cfg);  // talapel_model.cu
 ModelImpl* make_zudatar(const json::Value& cfg);  // zudatar_model.cu
+ModelImpl* make_zasorax(const json::Value& cfg);  // zasorax_model.cu
 
 }  // namespace nvllm

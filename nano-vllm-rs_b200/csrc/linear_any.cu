@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
         // bf16 models round gate and up to bf16 before the activation, as a separate projection would have
         float g = v, u = acu[i][j];
         if (sizeof(TI) == 2) { g = __bfloat162float(__float2bfloat16_rn(g)); u = __bfloat162float(__float2bfloat16_rn(u)); }
-        v = glu_clamped(g, u, a.limit);
+        v = a.act == 3 ? g / (1.0f + expf(-g)) * u : glu_clamped(g, u, a.limit);
       } else if (a.act == 2) {
         if (sizeof(TI) == 2) v = __bfloat162float(__float2bfloat16_rn(v));
         v = fmaxf(v, 0.f);
@@ -154,10 +154,16 @@ __global__ void glu_clamped_vec8_kernel(bf16* __restrict__ out, const bf16* __re
   }
 }
 
-// kind 0: out[i, c] = silu(in[i, c]) * in[i, ff + c] (in: [n, 2 ff]);  kind 1: out[i, c] = relu(in[i, c])^2 (in: [n, ff])
+// softplus without overflow: max(x, 0) + log1p(exp(-|x|))
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+// kind 0: out[i, c] = silu(in[i, c]) * in[i, ff + c] (in: [n, 2 ff]);  kind 1: out[i, c] = relu(in[i, c])^2 (in: [n, ff]);
+// kind 2: out[i, c] = xielu(in[i, c]) with the two learned numbers params[0..1] (in: [n, ff]):
+//         z > 0: softplus(p0) z^2 + z / 2;   z <= 0: (1/2 + softplus(p1)) (exp(z) - 1 - z) + z / 2
 template <typename T>
-__global__ void ff_activation_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t n, int ff, int kind) {
+__global__ void ff_activation_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t n, int ff, int kind, const float* __restrict__ params) {
   const int64_t total = n * ff;
+  const float ap = kind == 2 ? softplus_f(params[0]) : 0.f, an = kind == 2 ? 0.5f + softplus_f(params[1]) : 0.f;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / ff, c = i - r * ff;
@@ -165,6 +171,9 @@ __global__ void ff_activation_kernel(T* __restrict__ out, const T* __restrict__ 
     if (kind == 0) {
       const float g = ldf(in + r * 2 * ff + c);
       v = g / (1.0f + expf(-g)) * ldf(in + r * 2 * ff + ff + c);
+    } else if (kind == 2) {
+      const float z = ldf(in + i);
+      v = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
     } else {
       v = fmaxf(ldf(in + i), 0.f);
       v *= v;
@@ -306,9 +315,9 @@ extern "C" int nvllm_linear_grouped(void* y, const void* x, const void* w, int32
   NVLLM_CHECK_ARG(y && x && w, NVLLM_ERR_ARG, "linear_grouped: NULL");
   // GLU: every group's weight block is [gate rows (n) | up rows (n)] x k
   LinArgs a{y, x, w, max_rows, n, k, ldx, ldw, ldy, 0, group_stride_w, 0, row_src, tile_group,
-            static_cast<int64_t>(n) * ldw, limit, glu == 2 ? 2 : 0};
+            static_cast<int64_t>(n) * ldw, limit, glu == 2 ? 2 : (glu == 3 ? 3 : 0)};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return glu == 1 ? launch_tile<true>(a, max_rows / BM, 1, dtype, out_dtype, st)
+  return (glu == 1 || glu == 3) ? launch_tile<true>(a, max_rows / BM, 1, dtype, out_dtype, st)
              : launch_tile<false>(a, max_rows / BM, 1, dtype, out_dtype, st);
 }
 
@@ -335,7 +344,14 @@ extern "C" int nvllm_glu_clamped(void* out, const void* gate_up, int32_t n, int3
 }
 
 extern "C" int nvllm_ff_activation(void* out, const void* in, int32_t n, int32_t ff, int32_t kind, int32_t dtype, void* stream) {
-  NVLLM_CHECK_ARG(n >= 0 && ff > 0 && (kind == 0 || kind == 1), NVLLM_ERR_ARG, "ff_activation: n=%d ff=%d kind=%d", n, ff, kind);
+  NVLLM_CHECK_ARG(kind == 0 || kind == 1, NVLLM_ERR_ARG, "ff_activation: kind=%d", kind);
+  return nvllm_ff_activation_params(out, in, n, ff, kind, nullptr, dtype, stream);
+}
+
+extern "C" int nvllm_ff_activation_params(void* out, const void* in, int32_t n, int32_t ff, int32_t kind, const float* params, int32_t dtype,
+                                          void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && ff > 0 && kind >= 0 && kind <= 2 && (kind != 2 || params != nullptr), NVLLM_ERR_ARG,
+                  "ff_activation: n=%d ff=%d kind=%d (kind 2 needs its two parameters)", n, ff, kind);
   NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "ff_activation: dtype %d", dtype);
   if (n == 0) return 0;
   NVLLM_CHECK_ARG(out && in, NVLLM_ERR_ARG, "ff_activation: NULL");
@@ -343,8 +359,8 @@ extern "C" int nvllm_ff_activation(void* out, const void* in, int32_t n, int32_t
   int64_t blocks = (total + 255) / 256;
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == NVLLM_BF16) ff_activation_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(in), n, ff, kind);
-  else ff_activation_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), static_cast<const float*>(in), n, ff, kind);
+  if (dtype == NVLLM_BF16) ff_activation_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(in), n, ff, kind, params);
+  else ff_activation_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), static_cast<const float*>(in), n, ff, kind, params);
   NVLLM_LAUNCH_CHECK("ff_activation_kernel");
   return 0;
 }

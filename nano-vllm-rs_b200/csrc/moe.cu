@@ -67,6 +67,50 @@ __global__ void __launch_bounds__(128) moe_route_kernel(int32_t* __restrict__ id
   }
 }
 
+// Routing on the logits themselves: z = logits + bias; the `top` largest z (ties: lowest index); the weights are the softmax
+// over the chosen z alone.  One warp per token; z lives in shared memory ([warps][e_total]).
+__global__ void __launch_bounds__(128) moe_route_logits_kernel(int32_t* __restrict__ idx, float* __restrict__ wts,
+                                                               const float* __restrict__ logits, const float* __restrict__ bias,
+                                                               int64_t ld, int n, int e_total, int top) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n) return;
+  float* c = sm + static_cast<size_t>(warp) * e_total;
+  const float* z = logits + static_cast<int64_t>(t) * ld;
+  for (int e = lane; e < e_total; e += 32) c[e] = z[e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  float first = 0.f, wsum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < e_total; e += 32) {
+      const float v = c[e];
+      if (v > best) { best = v; bi = e; }   // ascending e per lane: the first maximum wins
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (bi == 0x7fffffff) { bi = 0; best = first; }  // every score NaN / -inf: degenerate, keep indices valid
+    if (k == 0) first = best;                        // the largest of all: the softmax's reference point
+    const float w = expf(best - first);
+    if (lane == 0) {
+      idx[static_cast<int64_t>(t) * top + k] = bi;
+      wts[static_cast<int64_t>(t) * top + k] = w;
+      c[bi] = -INFINITY;
+    }
+    wsum += w;
+    __syncwarp();
+  }
+  for (int k = lane; k < top; k += 32) {
+    const int64_t o = static_cast<int64_t>(t) * top + k;
+    wts[o] = wts[o] / wsum;
+  }
+}
+
 // Counting sort of the assignments by expert, one CTA.  Output layout: expert e owns rows [off[e], off[e] + cnt[e]) of the
 // grouped buffers, off[e] a multiple of the tile height so that no tile spans two experts.
 //   row_token[r]  token whose activations row r reads (-1: padding)
@@ -204,6 +248,18 @@ extern "C" int nvllm_moe_route(int32_t* topk_idx, float* topk_w, const float* lo
   const size_t smem = static_cast<size_t>(4) * 2 * e_total * sizeof(float);
   moe_route_kernel<<<(n + 3) / 4, 128, smem, static_cast<cudaStream_t>(stream)>>>(topk_idx, topk_w, logits, bias, n, e_total, top, scale);
   NVLLM_LAUNCH_CHECK("moe_route_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_moe_route_logits(int32_t* topk_idx, float* topk_w, const float* logits, int64_t ld, const float* bias, int32_t n,
+                                      int32_t experts, int32_t top, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && experts > 0 && top > 0 && top <= experts && experts <= 3072 && ld >= experts, NVLLM_ERR_ARG,
+                  "moe_route_logits: n=%d experts=%d top=%d", n, experts, top);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(topk_idx && topk_w && logits, NVLLM_ERR_ARG, "moe_route_logits: NULL");
+  const size_t smem = static_cast<size_t>(4) * experts * sizeof(float);
+  moe_route_logits_kernel<<<(n + 3) / 4, 128, smem, static_cast<cudaStream_t>(stream)>>>(topk_idx, topk_w, logits, bias, ld, n, experts, top);
+  NVLLM_LAUNCH_CHECK("moe_route_logits_kernel");
   return 0;
 }
 

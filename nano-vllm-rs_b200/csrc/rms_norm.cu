@@ -2,6 +2,7 @@
 //
 //   nvllm_rms_residual_norm   the fused step of a block with a norm before AND after every sublayer:
 //                                 h += rms(y) * post_w;   out = rms(h) * pre_w          rms(v) = v / sqrt(mean(v^2) + eps)
+//                             (pre_w == NULL: out = h, for blocks whose sublayers read the stream without a norm)
 //                             (the sublayer's output norm, the residual add and the next sublayer's input norm in one pass over
 //                             the row, as nvllm_dyt_residual_norm does for Dynamic Tanh models)
 //   nvllm_rms_norm_rows       rows of an f32 matrix, RMS-normed and weighted, written in the operand type to rows of a
@@ -67,6 +68,10 @@ __global__ void __launch_bounds__(256) rms_residual_norm_kernel(TO* __restrict__
     }
   }
   if (out == nullptr) return;
+  if (pre_w == nullptr) {   // no norm on the way out: the stream itself in the operand type
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) st_as(out, base + c, row[c]);
+    return;
+  }
   const float r = 1.0f / sqrtf(block_sum(sq, red) / hidden + eps);
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) st_as(out, base + c, row[c] * r * pre_w[c]);
 }
@@ -118,12 +123,12 @@ __global__ void __launch_bounds__(256) rms_residual_norm_vec_kernel(TO* __restri
     }
   }
   if (out == nullptr) return;
-  const float r = 1.0f / sqrtf(block_sum(sq, red) / hidden + eps);
+  const float r = pre_w != nullptr ? 1.0f / sqrtf(block_sum(sq, red) / hidden + eps) : 1.0f;   // pre_w == NULL: the stream itself
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const int c = threadIdx.x + 256 * k;
     if (c < nv) {
-      const float4 w = reinterpret_cast<const float4*>(pre_w)[c];
+      const float4 w = pre_w != nullptr ? reinterpret_cast<const float4*>(pre_w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
       const float4 o = make_float4(v[k].x * r * w.x, v[k].y * r * w.y, v[k].z * r * w.z, v[k].w * r * w.w);
       if (sizeof(TO) == 2) reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + base)[c] = make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
       else reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + base)[c] = o;
@@ -208,7 +213,7 @@ extern "C" int nvllm_rms_residual_norm(void* out, float* h, const void* y, int32
   NVLLM_CHECK_ARG((out_dtype == NVLLM_BF16 || out_dtype == NVLLM_F32) && (y_dtype == NVLLM_BF16 || y_dtype == NVLLM_F32), NVLLM_ERR_DTYPE,
                   "rms_residual_norm: dtype %d / %d", y_dtype, out_dtype);
   if (n == 0) return 0;
-  NVLLM_CHECK_ARG(h && (out || y) && (!y || post_w) && (!out || pre_w), NVLLM_ERR_ARG, "rms_residual_norm: NULL");
+  NVLLM_CHECK_ARG(h && (out || y) && (!y || post_w), NVLLM_ERR_ARG, "rms_residual_norm: NULL");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (hidden % 4 == 0 && hidden <= 8192 && aligned16(h) && aligned16(y) && aligned16(out) && aligned16(post_w) && aligned16(pre_w)) {
     const bool yb = y_dtype == NVLLM_BF16, ob = out_dtype == NVLLM_BF16;

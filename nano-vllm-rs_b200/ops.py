@@ -573,3 +573,79 @@ def gated_group_norm_act(y, gate, weight, parts, eps, gate_first, dtype, gate_ac
     check(_ffi.lib().nvllm_gated_group_norm_act(_p(out), out.stride(0), _p(y), y.stride(0), _p(gate), gate.stride(0), _p(weight), int(w_shared),
                                                 n, cols, parts, eps, int(gate_first), gate_act, _dt(out), _stream()))
     return out
+
+
+# ---- post-norm blocks, chunked attention with a distance bias, rotated values, xIELU, routing on logits (include/nvllm.h)
+
+
+def residual_cast(h, dtype):
+    """The f32 stream in the operand type (nvllm_rms_residual_norm without an incoming sublayer and without a norm)."""
+    n, hidden = h.shape
+    out = torch.empty((n, hidden), dtype=dtype, device=h.device)
+    check(_ffi.lib().nvllm_rms_residual_norm(_p(out), _p(h), None, F32, None, None, n, hidden, 1e-5, BF16 if dtype == torch.bfloat16 else F32,
+                                             _stream()))
+    return out
+
+
+def rms_residual_add(h, y, post_w, eps, dtype):
+    """h (f32, in place) += rms(y) * post_w; returns h in `dtype`."""
+    n, hidden = h.shape
+    out = torch.empty((n, hidden), dtype=dtype, device=h.device)
+    check(_ffi.lib().nvllm_rms_residual_norm(_p(out), _p(h), _p(y), _dt(y), _p(post_w), None, n, hidden, eps,
+                                             BF16 if dtype == torch.bfloat16 else F32, _stream()))
+    return out
+
+
+def attn_wide_norm_store(proj, q_cols, k_cols, v_cols, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots, dtype):
+    """proj: f32 [n, >= q + k + v columns].  Returns rms(q) * q_norm_w in `dtype`; rms(k) * k_norm_w and v go to cache rows `slots`."""
+    n = proj.shape[0]
+    q = torch.empty((n, q_cols), dtype=dtype, device=proj.device)
+    check(_ffi.lib().nvllm_attn_wide_norm_store(_p(q), q.stride(0), _p(k_cache), _p(v_cache), k_cache.stride(0) if k_cache is not None else 0,
+                                                v_cache.stride(0) if v_cache is not None else 0, _p(proj), proj.stride(0), _p(q_norm_w),
+                                                _p(k_norm_w), float(eps), _p(slots), n, q_cols, k_cols, v_cols, _dt(q), _stream()))
+    return q
+
+
+def attn_rotary_store(proj, heads, kv_heads, dim, vdim, positions, table, rot_dims, halves, v_table, norm_eps, k_cache, v_cache, slots, dtype,
+                      q_bias=None, k_bias=None, v_bias=None):
+    """attn_rope_norm_store with the pairing as a parameter and (v_table) values rotated over all of vdim before the store."""
+    n = proj.shape[0]
+    q = torch.empty((n, heads * dim), dtype=dtype, device=proj.device)
+    max_pos = table.shape[0] if table is not None else (v_table.shape[0] if v_table is not None else 1)
+    check(_ffi.lib().nvllm_attn_rotary_store(_p(q), q.stride(0), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(proj),
+                                             proj.stride(0), _p(q_bias), _p(k_bias), _p(v_bias), _p(positions), _p(table), rot_dims, int(halves),
+                                             _p(v_table), max_pos, float(norm_eps), _p(slots), n, heads, kv_heads, dim, vdim, 0, _dt(q),
+                                             _stream()))
+    return q
+
+
+def biased_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, block_size, heads, kv_heads, dim, vdim, scale, window=0,
+                     sinks=None, gate_per_head=False, chunk=0, head_scale=None, dist_bias=None, out_rot=None, cu_tokens=None):
+    """window_attention with a chunk mask, a factor per head, a distance-bias table [rows, heads] and an output rotation table."""
+    n = q.shape[0]
+    out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
+    check(_ffi.lib().nvllm_biased_attention(_p(out), out.stride(0), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                            int(gate_per_head), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(tok_seq),
+                                            _p(positions), _p(tables), tables.shape[1] if tables is not None else 1, block_size, n, heads,
+                                            kv_heads, dim, vdim, scale, 0.0, 0.0, 1, window, _p(sinks), chunk, _p(head_scale), _p(dist_bias),
+                                            dist_bias.shape[0] if dist_bias is not None else 0, _p(out_rot),
+                                            out_rot.shape[0] if out_rot is not None else 0, _p(cu_tokens),
+                                            cu_tokens.shape[0] - 1 if cu_tokens is not None else 0, _dt(q), _stream()))
+    return out
+
+
+def xielu(x, params):
+    """out = softplus(p0) x^2 + x / 2 for x > 0, (1/2 + softplus(p1)) (exp(x) - 1 - x) + x / 2 otherwise; params: f32 [2]."""
+    n, ff = x.shape
+    out = torch.empty((n, ff), dtype=x.dtype, device=x.device)
+    check(_ffi.lib().nvllm_ff_activation_params(_p(out), _p(x), n, ff, 2, _p(params), _dt(x), _stream()))
+    return out
+
+
+def moe_route_logits(logits, bias, top):
+    """The `top` largest of logits + bias (ties: lowest index) and the softmax over those alone."""
+    n, experts = logits.shape
+    idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(_ffi.lib().nvllm_moe_route_logits(_p(idx), _p(w), _p(logits), logits.stride(0), _p(bias), n, experts, top, _stream()))
+    return idx, w
