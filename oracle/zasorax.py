@@ -211,8 +211,8 @@ def chunk_attention_step(w, q_, m, eps, st, x, pos, own_kv):
     if own_kv:
         st.k.append((rms(w[q_ + "k"] @ x, eps) * w[q_ + "k.norm"]).reshape(G, D))
         st.v.append((w[q_ + "v"] @ x).reshape(G, V))
-    rel, size = w[q_ + "rel"], m["mask"]["size"]
-    first = pos // size * size
+    rel, size = w[q_ + "rel"], m.get("mask", {}).get("size", 0)
+    first = pos // size * size if size else 0          # no chunk size: plain causal
     out = np.zeros((H, V))
     for h in range(H):
         g = h // (H // G)

@@ -1,0 +1,660 @@
+"""GPU tests of the Zasorax architecture: every mechanism's kernel against plain numpy (float64) written from the equations
+(oracle/zasorax.py), then the engine — whole prompts, token-by-token decoding, portions down to two tokens, mixed batches
+with reused pages, chunk edges that pass over decoded tokens, greedy generation through LLMEngine.generate and a replay
+through bin/trace_run — on small random models.  f32 engines must agree with the oracle to rounding; bf16 engines within
+the error of bf16 operands.  Where random weights would hide a fault (one key among hundreds, a chunk's edge, a sink, a
+distance bias far away) the inputs are made so that one score stands out."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import zasorax as Z
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+F32 = torch.float32
+
+
+def within(e, dtype, sure=None, worst=0.2):
+    """f32: every position to rounding.  bf16: operand rounding through the layers of a narrow model scatters (a few
+    positions reach 0.1 of a row's spread, the typical one stays near 0.02); a wrong key, chunk or page moves rows by O(1).
+    sure (bf16 only): the number of leading positions whose expert choices are no close calls (see run_with_margins)."""
+    e = np.asarray(e)
+    if not np.isfinite(e).all():
+        return False
+    if dtype == "float32":
+        return e.max() < TOL[dtype]
+    e = e[:sure] if sure is not None else e
+    return len(e) == 0 or (e.max() < worst and e.mean() < 0.05)
+
+
+def run_with_margins(cfg, w, toks, floor=0.01):
+    """The oracle's logits, and how many leading positions are free of close calls: a router whose last chosen logit lies
+    within `floor` of the first one left out may choose otherwise under bf16 rounding, which moves that position (and, less,
+    the ones that later read it) by O(1) without anything being wrong."""
+    close, at = [], [0]
+    plain = Z.route
+
+    def spy(z, top):
+        s = np.sort(np.asarray(z))[::-1]
+        if top < len(s) and s[top - 1] - s[top] < floor:
+            close.append(at[0])
+        return plain(z, top)
+
+    Z.route = spy
+    try:
+        seq, out = Z.Sequence(cfg), []
+        for t, tok in enumerate(toks):
+            at[0] = t
+            out.append(Z.token_step(cfg, w, seq, int(tok)))
+    finally:
+        Z.route = plain
+    return np.stack(out), (min(close) if close else len(toks))
+
+
+def dev_t(a, dev, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev).to(dtype)
+
+
+def dev_i(a, dev, dtype=torch.int32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev).to(dtype)
+
+
+def rel_err(got, ref):
+    """Per row: rms of the centred difference over the rms of the centred reference."""
+    d = np.asarray(got, np.float64) - ref
+    d = d - d.mean(-1, keepdims=True)
+    r = ref - ref.mean(-1, keepdims=True)
+    return np.sqrt((d ** 2).mean(-1)) / np.sqrt((r ** 2).mean(-1))
+
+
+f32r = lambda x: np.asarray(x, np.float32).astype(np.float64)
+npf = lambda t: t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def rope_np(max_pos, dims, base):
+    """[max_pos, dims / 2, 2] of (cos, sin)(p * base^(-2i/dims)) — what the kernels read as their rotary table."""
+    p = np.arange(max_pos, dtype=np.float64)[:, None] * (float(base) ** (-2.0 * np.arange(dims // 2) / dims))[None, :]
+    return np.stack([np.cos(p), np.sin(p)], -1)
+
+
+# ------------------------------------------------------------------------------------------------ mechanisms alone
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hid", [50, 256, 1, 3000])
+def test_post_norm_residual_add(cuda, dtype, hid):
+    """x <- x + rms(y) w in f32, and the stream handed on in the operand type without any norm."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(hid)
+    n, eps = 7, 1e-5
+    h = rng.standard_normal((n, hid)) * 3
+    y = Z.bf16_round(rng.standard_normal((n, hid))) if dtype == torch.bfloat16 else f32r(rng.standard_normal((n, hid)))
+    w = f32r(1 + 0.3 * rng.standard_normal(hid))
+    hd = dev_t(h, cuda)
+    x0 = ops.residual_cast(hd, dtype)
+    np.testing.assert_array_equal(npf(x0), npf(hd.to(dtype)))
+    out = ops.rms_residual_add(hd, dev_t(y, cuda, dtype), dev_t(w, cuda), eps, dtype)
+    ref = np.stack([f32r(h[i]) + Z.rms(y[i], eps) * w for i in range(n)])
+    np.testing.assert_allclose(npf(hd), ref, rtol=2e-6, atol=2e-6)
+    np.testing.assert_array_equal(npf(out), npf(hd.to(dtype)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,D,V,own", [(4, 2, 6, 5, True), (8, 1, 96, 64, True), (3, 3, 10, 10, False), (1, 1, 1, 1, True)])
+def test_norm_over_the_whole_projection_and_store(cuda, dtype, H, G, D, V, own):
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(H * 100 + D)
+    n, eps, rows = 9, 1e-5, 40
+    qn, kn, vn = H * D, (G * D if own else 0), (G * V if own else 0)
+    ld = (qn + kn + vn + 7) // 8 * 8 + 8
+    proj = f32r(rng.standard_normal((n, ld)) * 2)
+    qw, kw = f32r(1 + 0.2 * rng.standard_normal(qn)), f32r(1 + 0.2 * rng.standard_normal(max(kn, 1)))
+    slots = rng.permutation(rows)[:n].astype(np.int32); slots[3] = -1
+    kc = torch.full((rows, max(kn, 1)), 7.0, device=cuda, dtype=dtype); vc = torch.full((rows, max(vn, 1)), 7.0, device=cuda, dtype=dtype)
+    q = ops.attn_wide_norm_store(dev_t(proj, cuda), qn, kn, vn, dev_t(qw, cuda), dev_t(kw, cuda) if own else None, eps,
+                                 kc if own else None, vc if own else None, dev_i(slots, cuda), dtype)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == F32 else dict(rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(npf(q), np.stack([Z.rms(proj[i, :qn], eps) * qw for i in range(n)]), **tol)   # ONE root mean square for all heads
+    if own:
+        kr, vr = np.full((rows, kn), 7.0), np.full((rows, vn), 7.0)
+        for i in range(n):
+            if slots[i] >= 0:
+                kr[slots[i]] = Z.rms(proj[i, qn:qn + kn], eps) * kw
+                vr[slots[i]] = proj[i, qn + kn:qn + kn + vn]
+        np.testing.assert_allclose(npf(kc), kr, **tol); np.testing.assert_allclose(npf(vc), vr, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,D,V,rot", [(4, 2, 8, 6, 4), (2, 1, 64, 64, 64), (3, 3, 10, 4, 0), (1, 1, 2, 2, 2), (5, 5, 12, 20, 6)])
+def test_rotary_halves_norm_and_rotated_values_store(cuda, dtype, H, G, D, V, rot):
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(H * 10 + D + rot)
+    n, eps, rows, base, max_pos = 11, 1e-5, 48, 50.0, 700
+    ld = (H * D + G * D + G * V + H + 7) // 8 * 8
+    proj = f32r(rng.standard_normal((n, ld)))
+    pos = rng.integers(0, max_pos, n); pos[0] = 0
+    slots = rng.permutation(rows)[:n].astype(np.int32); slots[5] = -1
+    tab = dev_t(rope_np(max_pos, rot, base), cuda) if rot else None
+    vtab = dev_t(rope_np(max_pos, V, base), cuda)
+    kc = torch.full((rows, G * D), 7.0, device=cuda, dtype=dtype); vc = torch.full((rows, G * V), 7.0, device=cuda, dtype=dtype)
+    q = ops.attn_rotary_store(dev_t(proj, cuda), H, G, D, V, dev_i(pos, cuda, torch.int64), tab, rot, True, vtab, eps, kc, vc, dev_i(slots, cuda), dtype)
+    tol = dict(rtol=2e-5, atol=2e-5) if dtype == F32 else dict(rtol=1e-2, atol=1e-2)
+    qr = np.stack([np.concatenate([Z.rms(Z.rotate_halves(proj[i, h * D:(h + 1) * D], pos[i], rot, base), eps) for h in range(H)]) for i in range(n)])
+    np.testing.assert_allclose(npf(q), qr, **tol)
+    kr, vr = np.full((rows, G * D), 7.0), np.full((rows, G * V), 7.0)
+    for i in range(n):
+        if slots[i] < 0:
+            continue
+        kr[slots[i]] = np.concatenate([Z.rms(Z.rotate_halves(proj[i, H * D + g * D:H * D + (g + 1) * D], pos[i], rot, base), eps) for g in range(G)])
+        o = H * D + G * D
+        vr[slots[i]] = np.concatenate([Z.rotate_halves(proj[i, o + g * V:o + (g + 1) * V], pos[i], V, base) for g in range(G)])
+    np.testing.assert_allclose(npf(kc), kr, **tol); np.testing.assert_allclose(npf(vc), vr, **tol)
+
+
+def _paged(rng, ctxs, bs, spare=3):
+    """Random page assignment: tables [seqs, cap], and for every (sequence, position) its cache slot."""
+    need = [(c + bs - 1) // bs for c in ctxs]
+    perm = rng.permutation(sum(need) + spare)
+    cap = max(need) + 1
+    tables = -np.ones((len(ctxs), cap), np.int32)
+    k = 0
+    for s, nb in enumerate(need):
+        tables[s, :nb] = perm[k:k + nb]; k += nb
+    slot = lambda s, p: int(tables[s, p // bs]) * bs + p % bs
+    return tables, slot, (sum(need) + spare) * bs
+
+
+def _attend(q, keys, vals, H, G, scale, pos, chunk=0, sink=None, temp=None, dist=None, gate=None, vrot=None):
+    """One token: q [H, D], keys / vals of positions 0..pos as [pos + 1, G, *].  dist: [rows, H], read at min(distance, rows - 1).
+    vrot = (vdim, base): the values are stored rotated by their position and the output is turned back by -pos."""
+    first = pos // chunk * chunk if chunk else 0
+    out = []
+    for h in range(H):
+        g = h // (H // G)
+        s = np.array([q[h] @ keys[j, g] * scale * (temp[h] if temp is not None else 1.0) +
+                      (dist[min(pos - j, dist.shape[0] - 1), h] if dist is not None else 0.0) for j in range(first, pos + 1)])
+        mx = max(s.max(), sink[h]) if sink is not None else s.max()
+        e = np.exp(s - mx)
+        p = e / (e.sum() + (np.exp(sink[h] - mx) if sink is not None else 0.0))
+        o = p @ vals[first:pos + 1, g]
+        if vrot is not None:
+            o = Z.rotate_halves(o, -pos, vrot[0], vrot[1])
+        out.append(o * (Z.sigmoid(gate[h]) if gate is not None else 1.0))
+    return np.concatenate(out)
+
+
+def _attention_case(cuda, rng, dtype, H, G, D, V, bs, chunk=0, with_dist=0, rotated=False, gate=False, steps=((0, 150), (37, 90), (149, 1), (64, 1), (63, 1))):
+    """One launch holding, per entry of `steps` (prefix length, new tokens), a whole prompt, portions after a cached prefix and
+    single tokens; pages in random order; returns (got, ref) rows."""
+    from nano_vllm_rs_b200 import ops
+    base, scale = 70.0, 0.3
+    ctxs = [p + n for p, n in steps]
+    tables, slot, rows = _paged(rng, ctxs, bs)
+    rnd = (lambda s: Z.bf16_round(rng.standard_normal(s))) if dtype == torch.bfloat16 else (lambda s: f32r(rng.standard_normal(s)))
+    keys = [rnd((c, G, D)) for c in ctxs]
+    raw_vals = [rnd((c, G, V)) for c in ctxs]
+    rot = lambda v, p: np.stack([Z.rotate_halves(v[g], p, V, base) for g in range(G)])
+    vals = [np.stack([rot(v[j], j) for j in range(len(v))]) if rotated else v for v in raw_vals]
+    if rotated and dtype == torch.bfloat16:
+        vals = [Z.bf16_round(v) for v in vals]
+    kc = torch.zeros((rows, G * D), device=cuda, dtype=dtype); vc = torch.zeros((rows, G * V), device=cuda, dtype=dtype)
+    for s, c in enumerate(ctxs):
+        idx = torch.tensor([slot(s, j) for j in range(c)], device=cuda)
+        kc[idx] = dev_t(keys[s].reshape(c, -1), cuda, dtype); vc[idx] = dev_t(vals[s].reshape(c, -1), cuda, dtype)
+    tok_seq = np.concatenate([[s] * n for s, (_, n) in enumerate(steps)]).astype(np.int32)
+    pos = np.concatenate([np.arange(p, p + n) for p, n in steps]).astype(np.int64)
+    cu = np.concatenate([[0], np.cumsum([n for _, n in steps])]).astype(np.int32)
+    q = rnd((len(pos), H, D))
+    sink = f32r(rng.standard_normal(H)) if not rotated else np.zeros(H)
+    temp = f32r(1 + 0.3 * rng.standard_normal(H)) if not rotated else None
+    dist = f32r(rng.standard_normal((with_dist, H))) if with_dist else None
+    gt = f32r(rng.standard_normal((len(pos), H))) if gate else None
+    got = ops.biased_attention(dev_t(q.reshape(len(pos), -1), cuda, dtype), dev_t(gt, cuda) if gate else None, kc, vc, dev_i(tok_seq, cuda),
+                               dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs, H, G, D, V, scale, sinks=dev_t(sink, cuda),
+                               gate_per_head=gate, chunk=chunk, head_scale=dev_t(temp, cuda) if temp is not None else None,
+                               dist_bias=dev_t(dist, cuda) if with_dist else None,
+                               out_rot=dev_t(rope_np(int(pos.max()) + 5, V, base), cuda) if rotated else None, cu_tokens=dev_i(cu, cuda))
+    ref = np.stack([_attend(q[t], keys[tok_seq[t]], vals[tok_seq[t]], H, G, scale, int(pos[t]), chunk, sink, temp, dist,
+                            gt[t] if gate else None, (V, base) if rotated else None) for t in range(len(pos))])
+    return npf(got), ref
+
+
+CHUNK_CASES = [  # heads, kv heads, dim, vdim, chunk, page, rows of the distance table
+    (4, 2, 6, 5, 7, 16, 5), (8, 1, 96, 64, 64, 64, 64), (4, 2, 64, 64, 33, 16, 300), (2, 2, 128, 128, 70, 32, 20), (3, 1, 16, 8, 1, 16, 1),
+    (6, 3, 32, 32, 64, 16, 10), (2, 1, 8, 24, 0, 16, 200), (16, 2, 64, 32, 50, 64, 50),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", CHUNK_CASES)
+def test_chunked_attention_with_distance_bias_temperature_and_sink(cuda, dtype, case):
+    H, G, D, V, chunk, bs, rows = case
+    got, ref = _attention_case(cuda, np.random.default_rng(sum(case)), dtype, H, G, D, V, bs, chunk=chunk, with_dist=rows)
+    tol = 2e-5 if dtype == F32 else 2e-2
+    assert np.abs(got - ref).max() < tol * max(1.0, np.abs(ref).max()), np.abs(got - ref).max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,D,V,bs", [(4, 2, 8, 6, 16), (4, 2, 64, 64, 64), (2, 1, 128, 128, 16), (3, 3, 16, 40, 32), (8, 2, 96, 64, 16), (1, 1, 2, 2, 16)])
+def test_attention_over_rotated_values_turns_the_output_back(cuda, dtype, H, G, D, V, bs):
+    got, ref = _attention_case(cuda, np.random.default_rng(H + D + V), dtype, H, G, D, V, bs, rotated=True, gate=True)
+    tol = 2e-5 if dtype == F32 else 2e-2
+    assert np.abs(got - ref).max() < tol * max(1.0, np.abs(ref).max()), np.abs(got - ref).max()
+
+
+def _standout(cuda, dtype, p, portion, chunk, bs, hot=None, sink=None, dist=None):
+    """One sequence of p + 1 tokens whose last `portion` tokens are the step; weak random keys, except that key `hot` is made
+    to score +40 against the query at position p.  Returns (kernel row, reference row, values) for position p."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(p * 7 + portion + chunk)
+    H, G, D, V, scale = 2, 1, 16, 8, 0.25
+    rnd = (lambda s: Z.bf16_round(rng.standard_normal(s))) if dtype == torch.bfloat16 else (lambda s: f32r(rng.standard_normal(s)))
+    ctx = p + 1
+    keys, vals, q = rnd((ctx, G, D)) * 0.05, rnd((ctx, G, V)), rnd((portion, H, D))
+    keys = Z.bf16_round(keys) if dtype == torch.bfloat16 else keys
+    q[-1, 1] = q[-1, 0]
+    if hot is not None:
+        keys[hot, 0] = q[-1, 0] * (40.0 / (q[-1, 0] @ q[-1, 0] * scale))
+        keys = Z.bf16_round(keys) if dtype == torch.bfloat16 else f32r(keys)
+    tables, slot, rows = _paged(rng, [ctx], bs)
+    kc = torch.zeros((rows, G * D), device=cuda, dtype=dtype); vc = torch.zeros((rows, G * V), device=cuda, dtype=dtype)
+    idx = torch.tensor([slot(0, j) for j in range(ctx)], device=cuda)
+    kc[idx] = dev_t(keys.reshape(ctx, -1), cuda, dtype); vc[idx] = dev_t(vals.reshape(ctx, -1), cuda, dtype)
+    pos = np.arange(ctx - portion, ctx).astype(np.int64)
+    sk = np.full(H, sink if sink is not None else -30.0)
+    got = ops.biased_attention(dev_t(q.reshape(portion, -1), cuda, dtype), None, kc, vc, dev_i(np.zeros(portion, np.int32), cuda),
+                               dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs, H, G, D, V, scale, sinks=dev_t(sk, cuda), chunk=chunk,
+                               dist_bias=dev_t(dist, cuda) if dist is not None else None, cu_tokens=dev_i(np.array([0, portion], np.int32), cuda))
+    ref = _attend(q[-1], keys, vals, H, G, scale, p, chunk, sk, None, dist)
+    return npf(got)[-1], ref, vals
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("portion", [1, 2, 40])
+@pytest.mark.parametrize("chunk,bs,p", [(64, 64, 200), (64, 16, 191), (64, 16, 192), (5, 16, 33), (70, 32, 150), (33, 16, 131), (1, 16, 40)])
+def test_chunk_edges_stand_out(cuda, dtype, chunk, bs, p, portion):
+    """The first key of the query's chunk takes all the mass when it is made to; the key just before it (the last one of the
+    chunk before, often on another page) gets none whatever it would score; so with the query's own key."""
+    tol = 1e-4 if dtype == F32 else 3e-2
+    first = p // chunk * chunk
+    got, ref, vals = _standout(cuda, dtype, p, portion, chunk, bs, hot=first)
+    assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[first, 0]).max() < tol
+    if first > 0:
+        got, ref, vals = _standout(cuda, dtype, p, portion, chunk, bs, hot=first - 1)
+        assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[first - 1, 0]).max() > 0.1
+    got, ref, vals = _standout(cuda, dtype, p, portion, chunk, bs, hot=p)
+    assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[p, 0]).max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("portion", [1, 30])
+def test_sink_and_far_distance_bias_stand_out(cuda, dtype, portion):
+    tol = 1e-4 if dtype == F32 else 3e-2
+    got, ref, _ = _standout(cuda, dtype, 100, portion, 0, 16, sink=60.0)          # a sink of +60 takes all the mass and gives no value
+    assert np.abs(got).max() < 1e-6 and np.abs(ref).max() < 1e-6
+    got, ref, _ = _standout(cuda, dtype, 100, portion, 0, 16, hot=3, sink=0.0)    # a key 97 tokens back against a sink of score 0
+    assert np.abs(got - ref).max() < tol
+    dist = np.zeros((90, 2)); dist[77] = 50.0                                      # one distance stands out: key 100 - 77
+    got, ref, vals = _standout(cuda, dtype, 100, portion, 0, 16, dist=dist)
+    assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[23, 0]).max() < tol
+    dist = np.zeros((51, 2)); dist[50] = 50.0                                      # the last row serves every larger distance: keys 0 .. 50
+    got, ref, vals = _standout(cuda, dtype, 100, portion, 0, 16, dist=dist)
+    assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[:51, 0].mean(0)).max() < 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_xielu(cuda, dtype):
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((13, 37)) * 3
+    x = Z.bf16_round(x) if dtype == torch.bfloat16 else f32r(x)
+    for p, q in ((0.3, -0.7), (-4.0, 5.0), (0.0, 0.0)):
+        got = ops.xielu(dev_t(x, cuda, dtype), dev_t(np.array([p, q]), cuda))
+        ref = Z.xielu(x, p, q)
+        np.testing.assert_allclose(npf(got), ref, rtol=1e-5 if dtype == F32 else 1e-2, atol=1e-6 if dtype == F32 else 1e-2)
+
+
+@pytest.mark.parametrize("E,top", [(5, 2), (8, 4), (1, 1), (40, 40), (70, 3)])
+def test_routing_on_logits(cuda, E, top):
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(E)
+    n = 50
+    z = f32r(rng.standard_normal((n, E)) * 2)
+    b = f32r(rng.standard_normal(E))
+    if E > 2:
+        z[0, :] = 0.0                                 # row 0: only the bias decides
+        b[2] = b[0]; z[1, 2] = z[1, 0] = 9.0          # row 1: experts 0 and 2 tie at the top; 0 comes first
+    pad = torch.zeros((n, E + 3), device=cuda); pad[:, :E] = dev_t(z, cuda)
+    idx, w = ops.moe_route_logits(pad[:, :E], dev_t(b, cuda), top)     # rows E + 3 apart
+    idx, w = idx.cpu().numpy(), npf(w)
+    for t in range(n):
+        ri, rw = Z.route(f32r(z[t] + b), top)
+        assert idx[t].tolist() == ri, t
+        np.testing.assert_allclose(w[t], rw, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_experts_with_the_plain_silu_gate(cuda, dtype):
+    """Tokens grouped by expert, [gate | up] product with silu(g) * u in the tile kernel's epilogue, down product, weighted sum."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(9)
+    n, W, ff, E, top = 21, 24, 10, 5, 2
+    rnd = (lambda s, sc=1.0: Z.bf16_round(rng.standard_normal(s) * sc)) if dtype == torch.bfloat16 else (lambda s, sc=1.0: f32r(rng.standard_normal(s) * sc))
+    x, gu, dn = rnd((n, W)), rnd((E, 2 * ff, W), 0.3), rnd((E, W, ff), 0.3)
+    z = f32r(rng.standard_normal((n, E)))
+    idx, wts = ops.moe_route_logits(dev_t(z, cuda), None, top)
+    row_token, tile_expert, slot_row = ops.moe_sort(idx, E)
+    rows = row_token.shape[0]
+    xd = dev_t(x, cuda, dtype)
+    act = ops.linear_grouped(xd, dev_t(gu.reshape(E * 2 * ff, W), cuda, dtype), row_token, tile_expert, rows, ff, W, 2 * ff * W, glu=3)
+    eo = ops.linear_grouped(act, dev_t(dn.reshape(E * W, ff), cuda, dtype), None, tile_expert, rows, W, ff, W * ff)
+    got = npf(ops.moe_combine(eo, xd, None, idx, wts, slot_row, E))
+    ref = np.zeros((n, W))
+    for t in range(n):
+        ri, rw = Z.route(z[t], top)
+        for e, g in zip(ri, rw):
+            a = gu[e, :ff] @ x[t]
+            ref[t] += g * (dn[e] @ (a * Z.sigmoid(a) * (gu[e, ff:] @ x[t])))
+    np.testing.assert_allclose(got, ref, rtol=1e-4 if dtype == F32 else 3e-2, atol=1e-4 if dtype == F32 else 3e-2)
+
+
+# ------------------------------------------------------------------------------------------------ the engine
+
+def variant(name):
+    C, R = Z.chunk_mixer, Z.rotary_mixer
+    if name == "all_kinds":      # both mixers, grouped heads, sizes all different, every feed-forward kind, a layer that reads layer 1's keys
+        return Z.make_config([("attention_2", R(), Z.dense_mlp(20)), ("attention", C(), Z.expert_mlp()),
+                              ("attention_2", R(heads=2, kv_heads=1, dim=6, vdim=10, rot_dims=6, rot_base=1e4, scale=0.5), None),
+                              ("attention", C(heads=6, kv_heads=2, chunk=11, scale=0.2, bias_max=9, kv_from=1), Z.expert_mlp(ff=6, experts=3, top=3)),
+                              ("attention", C(heads=3, kv_heads=3, dim=4, vdim=7, chunk=16, bias_max=40), Z.dense_mlp(12))]), {1: 8, 3: 4, 4: 12}
+    if name == "ones":           # sizes that are 1 or equal to one another: one head, chunks of one and of everything, one expert, no rotation
+        return Z.make_config([("attention", C(heads=1, kv_heads=1, dim=1, vdim=1, chunk=1, scale=1.0, bias_max=3), Z.expert_mlp(ff=1, experts=1, top=1)),
+                              ("attention_2", R(heads=1, kv_heads=1, dim=2, vdim=2, rot_dims=0, scale=1.0), None),
+                              ("attention", C(heads=2, kv_heads=2, dim=8, vdim=8, chunk=1000, scale=1.0, bias_max=2000), Z.dense_mlp(1)),
+                              ("attention_2", R(heads=3, kv_heads=3, dim=8, vdim=8, rot_dims=8, rot_base=1.0), Z.expert_mlp(ff=8, experts=2, top=2))],
+                             width=16, vocab=33, embed_scale=1.0), {0: 2, 2: 6}
+    if name == "tensor_core":    # sizes the tensor-core kernels accept (bf16): width and inner sizes multiples of 64, heads of 64 / 96 / 128
+        return Z.make_config([("attention_2", R(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, rot_base=1e4, scale=0.1), Z.expert_mlp(ff=64, experts=4, top=2)),
+                              ("attention", C(heads=4, kv_heads=1, dim=96, vdim=64, chunk=64, scale=0.1, bias_max=100), Z.dense_mlp(128)),
+                              ("attention_2", R(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=128, rot_base=500.0, scale=0.09), None),
+                              ("attention", C(heads=2, kv_heads=1, dim=96, vdim=64, chunk=40, scale=0.1, bias_max=30, kv_from=1), Z.expert_mlp(ff=128, experts=3, top=1))],
+                             width=64, vocab=96), {1: 16, 3: 10}
+    raise KeyError(name)
+
+
+VARIANTS = ["all_kinds", "ones", "tensor_core"]
+
+
+def model_for(name, rng):
+    cfg, rel_rows = variant(name)
+    return cfg, Z.random_weights(cfg, rng, rel_rows=rel_rows)
+
+
+def make_engine(tmp_path, cfg, w, dtype, bs=16, blocks=24, max_seqs=4, eager=1):
+    from nano_vllm_rs_b200.engine import LLMEngine
+    from nano_vllm_rs_b200.loader import write_safetensors
+    d = tmp_path / ("m_" + dtype)
+    d.mkdir(exist_ok=True)
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(d / "model.safetensors"), {k: Z.to_bf16_bits(v) for k, v in w.items()})
+    return LLMEngine.from_pretrained(str(d), dtype=dtype, kvcache_block_size=bs, num_kvcache_blocks=blocks, max_num_seqs=max_seqs,
+                                     max_num_batched_tokens=blocks * bs, max_model_len=blocks * bs, enforce_eager=eager), str(d)
+
+
+def replay(eng, requests, schedule):
+    """schedule: list of steps, each a list of (request index, token count).  Returns every position's logits per request."""
+    from nano_vllm_rs_b200.engine import SamplingParams
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+    sid, at, out = {}, {}, {i: [] for i in range(len(requests))}
+    for step in schedule:
+        ids, counts = [], []
+        for i, c in step:
+            toks = requests[i][at.get(i, 0):at.get(i, 0) + c]
+            if i in sid:
+                eng.scheduler.extend_sequence(sid[i], toks)
+            else:
+                sid[i] = eng.scheduler.add_sequence(toks, sp)
+            ids.append(sid[i]); counts.append(c)
+        lg = eng.step_chunks(ids, counts, list(range(sum(counts))))
+        k = 0
+        for i, c in step:
+            out[i].append(lg[k:k + c]); k += c
+            at[i] = at.get(i, 0) + c
+            if at[i] == len(requests[i]):
+                eng.scheduler.finish_sequence(sid[i]); eng.scheduler.release_sequence(sid[i])
+                del sid[i]
+    return {i: np.concatenate(v) for i, v in out.items()}
+
+
+def cut(n, sizes):
+    out, k = [], 0
+    while n > 0:
+        c = min(n, sizes[k % len(sizes)]); out.append(c); n -= c; k += 1
+    return out
+
+
+def greedy(cfg, w, prompt, n_new):
+    """The oracle's greedy continuation and the top-1 / top-2 margin of every step (relative to the row's spread)."""
+    seq, out, margins, lg = Z.Sequence(cfg), [], [], None
+    for t in prompt:
+        lg = Z.token_step(cfg, w, seq, int(t))
+    for _ in range(n_new):
+        o = np.argsort(lg)
+        out.append(int(o[-1])); margins.append((lg[o[-1]] - lg[o[-2]]) / lg.std())
+        lg = Z.token_step(cfg, w, seq, out[-1])
+    return out, margins
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", VARIANTS)
+def test_engine_schedules_match_the_oracle(cuda, tmp_path, name, dtype):
+    rng = np.random.default_rng(300 + VARIANTS.index(name))
+    cfg, w = model_for(name, rng)
+    lens = [1, 2, 37, 90, 33]
+    reqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in lens]
+    ref, sure = zip(*[run_with_margins(cfg, w, r) for r in reqs])
+    assert sum(sure) > 0.5 * sum(lens)
+    eng, _ = make_engine(tmp_path, cfg, w, dtype, bs=16, blocks=12)    # 192 slots: the requests only fit one after another
+    worst = 0.35 if name == "ones" else 0.2       # two-value heads behind an output norm: a small head output has no stable direction
+
+    def check(got, what):
+        for i, r in enumerate(ref):
+            e = rel_err(got[i], r)
+            assert within(e, dtype, sure[i], worst), f"{name} {dtype} {what}: request {i} position {int(e.argmax())} error {e.max():.3g}"
+
+    whole = replay(eng, reqs, [[(i, len(r))] for i, r in enumerate(reqs)])
+    check(whole, "whole prompts")
+    # most of the prompt at once, the last tokens one by one (chunk edges pass under decoded tokens and page borders)
+    dec = replay(eng, reqs, [s for i, r in enumerate(reqs) for s in ([[(i, max(1, len(r) - 50))]] + [[(i, 1)]] * (len(r) - max(1, len(r) - 50)))])
+    check(dec, "prefill + single tokens")
+    one = replay(eng, reqs[:3], [[(i, 1)] for i, r in enumerate(reqs[:3]) for _ in r])
+    for i in range(3):
+        assert within(rel_err(one[i], ref[i]), dtype, sure[i], worst)
+    # portions of changing size down to two tokens (across pages and chunk edges)
+    por = replay(eng, reqs, [[(i, c)] for i, r in enumerate(reqs) for c in cut(len(r), [2, 5, 16, 3, 17, 2, 31])])
+    check(por, "portions")
+    for i in range(len(reqs)):  # a position must not depend on how the prompt was cut, beyond rounding
+        n = len(reqs[i]) if dtype == "float32" else sure[i]
+        if n > 0:
+            assert rel_err(por[i][:n], whole[i][:n].astype(np.float64)).max() < (1e-4 if dtype == "float32" else worst)
+            assert rel_err(dec[i][:n], whole[i][:n].astype(np.float64)).max() < (1e-4 if dtype == "float32" else worst)
+
+
+def test_engine_layer_taps_match_the_oracle(cuda, tmp_path):
+    """The residual stream after every layer, for a prompt: each mixer and feed-forward kind is checked where it sits."""
+    rng = np.random.default_rng(31)
+    cfg, w = model_for("all_kinds", rng)
+    toks = rng.integers(0, cfg["vocab"], 30).tolist()
+    _, taps = Z.run_sequence(cfg, w, toks, layer_taps=True)
+    eng, _ = make_engine(tmp_path, cfg, w, "float32")
+    from nano_vllm_rs_b200.engine import SamplingParams
+    tap = eng.model_runner.layer_tap(len(toks))
+    sid = eng.scheduler.add_sequence(toks, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+    eng.step_chunks([sid], [len(toks)], [0])
+    for i in range(len(cfg["layers"])):
+        np.testing.assert_allclose(tap[i], taps[i], rtol=2e-4, atol=2e-4, err_msg="after layer %d" % i)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_engine_mixed_batches_reuse_pages(cuda, tmp_path, dtype):
+    """Up to four live requests per step, portions of some beside single tokens of others, in a pool that only holds them
+    because finished requests give their pages back; every request equals its run alone and the oracle."""
+    rng = np.random.default_rng(32)
+    cfg, w = model_for("all_kinds", rng)
+    lens = [50, 23, 64, 9, 41, 30, 17]
+    reqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in lens]
+    ref, sure = zip(*[run_with_margins(cfg, w, r) for r in reqs])
+    assert sum(sure) > 0.5 * sum(lens)
+    eng, _ = make_engine(tmp_path, cfg, w, dtype, bs=16, blocks=11, max_seqs=4)   # 176 slots < 234 tokens in total
+    need = [(n + 15) // 16 for n in lens]
+    at, live, nxt, sched, k = [0] * len(lens), [], 0, [], 0
+    while nxt < len(reqs) or live:
+        while nxt < len(reqs) and len(live) < 4 and sum(need[i] for i in live) + need[nxt] <= 11:
+            live.append(nxt); nxt += 1
+        step = []
+        for i in live:
+            k += 1
+            if k % 5 == 0 and len(live) > 1:
+                continue                                  # a live request may sit a step out
+            c = 1 if (at[i] > lens[i] // 2 or k % 3 == 0) else [2, 7, 16, 5][k % 4]
+            c = min(c, lens[i] - at[i])
+            step.append((i, c)); at[i] += c
+        if step:
+            sched.append(step)
+        live = [i for i in live if at[i] < lens[i]]
+    assert any(len(s) == 4 for s in sched) and any(len({c for _, c in s}) > 1 for s in sched)
+    mixed = replay(eng, reqs, sched)
+    st = eng.scheduler.get_stats()
+    assert st["free_blocks"] == st["total_blocks"] == 11
+    alone = replay(eng, reqs, [[(i, len(r))] for i, r in enumerate(reqs)])
+    for i, r in enumerate(ref):
+        assert within(rel_err(mixed[i], r), dtype, sure[i]), (i, rel_err(mixed[i], r).max())
+        n = lens[i] if dtype == "float32" else sure[i]
+        if n > 0:
+            assert rel_err(mixed[i][:n], alone[i][:n].astype(np.float64)).max() < (1e-4 if dtype == "float32" else 0.2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_engine_long_decoding_over_many_pages(cuda, tmp_path, dtype):
+    """300 tokens at once, then 80 one by one over 20+ pages: chunks of 70 and 33 start under decoded tokens and in the
+    middle of pages, the causal layer reads keys hundreds of tokens back, and the distance table is read past its last step."""
+    rng = np.random.default_rng(33)
+    cfg = Z.make_config([("attention", Z.chunk_mixer(chunk=70, bias_max=50), Z.expert_mlp()), ("attention_2", Z.rotary_mixer(), None),
+                         ("attention", Z.chunk_mixer(heads=2, kv_heads=2, chunk=33, bias_max=20, kv_from=0), Z.dense_mlp(16)),
+                         ("attention", Z.chunk_mixer(chunk=0, bias_max=300), None)])
+    w = Z.random_weights(cfg, rng, rel_rows={0: 10, 2: 6, 3: 16})
+    toks = rng.integers(0, cfg["vocab"], 380).tolist()
+    ref, sure = run_with_margins(cfg, w, toks, floor=0.0 if dtype == "float32" else 0.02)
+    eng, _ = make_engine(tmp_path, cfg, w, dtype, bs=16, blocks=24, max_seqs=2)
+    got = replay(eng, [toks], [[(0, 300)]] + [[(0, 1)]] * 80)
+    e = rel_err(got[0], ref)
+    if dtype == "float32":
+        assert e.max() < TOL[dtype], (int(e.argmax()), e.max())
+    else:   # a close call of the router moves single rows; keys, chunks and pages that went wrong would move most of them
+        assert np.isfinite(e).all() and np.median(e) < 0.05 and (e > 0.2).mean() < 0.1, (np.median(e), (e > 0.2).mean())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(cuda, tmp_path, dtype):
+    """LLMEngine.generate: the scheduler's own prefill / decode batches, decode steps replayed as CUDA graphs, pages taken
+    while decoding, six prompts for four sequences at a time."""
+    from nano_vllm_rs_b200.engine import SamplingParams
+    rng = np.random.default_rng(34)
+    cfg, w = model_for("all_kinds", rng)
+    prompts = [rng.integers(0, cfg["vocab"], n).tolist() for n in (5, 1, 30, 16, 3, 20)]
+    n_new = 40
+    eng, _ = make_engine(tmp_path, cfg, w, dtype, bs=16, blocks=40, max_seqs=4, eager=0)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    margin_floor = 1e-3 if dtype == "float32" else 0.15
+    agreed = 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == n_new
+        ref, margins = greedy(cfg, w, p, n_new)
+        for j in range(n_new):
+            if o[j] != ref[j]:
+                assert margins[j] < margin_floor, (j, margins[j])   # a near-tie may fall either way; later tokens then differ
+                break
+            agreed += 1
+    assert agreed > 0.6 * n_new * len(prompts)
+    st = eng.scheduler.get_stats()
+    assert st["decode_batches"] >= n_new - 1 and st["free_blocks"] == st["total_blocks"]
+
+
+def test_generation_shares_prompt_pages_and_survives_preemption(cuda, tmp_path):
+    """Four prompts with a common first page in a pool too small for them to grow: shared pages are read by all, the scheduler
+    preempts and later recomputes a victim from position 0; the tokens stay the oracle's."""
+    from nano_vllm_rs_b200.engine import SamplingParams
+    rng = np.random.default_rng(35)
+    cfg, w = model_for("all_kinds", rng)
+    head = rng.integers(0, cfg["vocab"], 16).tolist()
+    prompts = [head + rng.integers(0, cfg["vocab"], n).tolist() for n in (1, 6, 3, 9)]
+    n_new = 40
+    eng, _ = make_engine(tmp_path, cfg, w, "float32", bs=16, blocks=10, max_seqs=4, eager=0)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    st = eng.scheduler.get_stats()
+    assert st["preemptions"] > 0 and st["free_blocks"] == st["total_blocks"]
+    for p, o in zip(prompts, outs):
+        ref, margins = greedy(cfg, w, p, n_new)
+        for j in range(n_new):
+            if o[j] != ref[j]:
+                assert margins[j] < 1e-3, (j, margins[j])
+                break
+
+
+def test_synthetic_weights_and_command_line(cuda, tmp_path):
+    """Seeded synthetic weights (no checkpoint) run a step; `python -m nano_vllm_rs_b200 generate` on a checkpoint gives the
+    oracle's greedy tokens and, with a temperature, draws of the device sampler; the registry lists the architecture."""
+    import sys
+    from nano_vllm_rs_b200.engine import Config, LLMEngine, SamplingParams
+    rng = np.random.default_rng(36)
+    cfg, _ = variant("tensor_core")
+    eng = LLMEngine(Config(model_config=cfg, dtype="bfloat16", kvcache_block_size=16, num_kvcache_blocks=8, max_num_seqs=2,
+                                     max_num_batched_tokens=128, max_model_len=128, enforce_eager=1), init_weights=True)
+    sid = eng.scheduler.add_sequence(rng.integers(0, cfg["vocab"], 20).tolist(), SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+    lg = eng.step_chunks([sid], [20], [19])
+    assert np.isfinite(lg).all() and lg.std() > 0
+    cfg, w = model_for("all_kinds", rng)
+    _, model_dir = make_engine(tmp_path, cfg, w, "float32")
+    prompt = rng.integers(0, cfg["vocab"], 9).tolist()
+    run = lambda *extra: subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "generate", "--model", model_dir, "--dtype", "float32", "--prompt-ids",
+                                         ",".join(map(str, prompt)), "--max-tokens", "12", "--block-size", "16", *extra], cwd=ROOT, capture_output=True,
+                                        text=True, timeout=600)
+    r = run()
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    ref, margins = greedy(cfg, w, prompt, 12)
+    for j in range(12):
+        if out["completion_ids"][j] != ref[j]:
+            assert margins[j] < 1e-3
+            break
+    r = run("--temperature", "1.5", "--top-k", "20")      # the device sampler draws from the same logits
+    assert r.returncode == 0, r.stderr[-2000:]
+    sampled = json.loads(r.stdout.strip().splitlines()[-1])["completion_ids"]
+    assert len(sampled) == 12 and all(0 <= t < cfg["vocab"] for t in sampled) and sampled != ref
+    r = subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "architectures"], cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert "Zasorax" in r.stdout
+
+
+def test_trace_run_replays_a_schedule(cuda, tmp_path):
+    rng = np.random.default_rng(37)
+    cfg, w = model_for("all_kinds", rng)
+    _, model_dir = make_engine(tmp_path, cfg, w, "float32")
+    a, b = rng.integers(0, cfg["vocab"], 70).tolist(), rng.integers(0, cfg["vocab"], 9).tolist()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [0, 39]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[:8], "want": []}, {"id": "a", "tokens": a[40:69], "want": [28]}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}, {"id": "b", "tokens": b[8:], "want": [0]}], "end": ["a", "b"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": b, "want": [8]}], "end": ["c"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    ra, rb = Z.run_sequence(cfg, w, a), Z.run_sequence(cfg, w, b)
+    rd = lambda n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+    for got, ref in ((rd(0), ra[[0, 39]]), (rd(1), ra[[68]]), (rd(2), np.stack([ra[69], rb[8]])), (rd(3), rb[[8]])):
+        assert got.shape == ref.shape and rel_err(got, ref).max() < TOL["float32"]
