@@ -53,12 +53,13 @@ def parse():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=None, help="override the workload model (qwen3-0.6b | qwen3-8b | qwen3-32b)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen", "talapel", "zudatar"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen", "talapel", "zudatar", "zasorax"],
                     help="kosazen: prefill / decode throughput and a per-kernel roofline table of the Kosazen architecture "
                          "(latent attention + mixture of experts) beside Qwen3 models of equal layer sizes, random weights; "
                          "talapel: the same for the Talapel architecture (capped attention beside a state-space mixer, retention, "
                          "table-routed experts); zudatar: the same for the Zudatar architecture (windowed attention, latent "
-                         "attention in a window, gated delta rule)")
+                         "attention in a window, gated delta rule); zasorax: the same for the Zasorax architecture (post-norm blocks, "
+                         "chunked attention with a distance bias, rotated values, experts routed on logits)")
     ap.add_argument("--seqs", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the in-run parity checks (profiling runs)")
@@ -772,6 +773,29 @@ def zudatar_config(z):
             "layers": [kinds[i % 4] for i in range(z["layers"])]}
 
 
+# Zasorax: post-norm blocks; a rotary layer with rotated values and a dense xIELU feed-forward, a chunked layer with a distance
+# bias and experts, a rotary layer with experts, and a chunked layer that reads the second one's keys and values; chunks half
+# the prompt.  The Qwen3 arm: same width, depth, query / kv heads of 128, and a gated MLP with the mean multiply-adds per token.
+ZASORAX_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=512, rot_dims=64, bias_rows=32, bias_max=1024, dense_ff=8192, ff=1024,
+                  experts=32, top=4, layers=4, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=512, rot_dims=64, bias_rows=32, bias_max=1024, dense_ff=12288, ff=1536,
+                  experts=32, top=4, layers=4, vocab=32768),
+}
+
+
+def zasorax_config(z):
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    rot = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+           "rot": {"base": 10000.0, "dims": z["rot_dims"]}}
+    chk = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "mask": {"size": z["chunk"]},
+           "bias_max": z["bias_max"], "bias_rows": z["bias_rows"]}
+    kinds = [{"type": "attention_2", "mixer": rot, "mlp": {"kind": "dense", "ff": z["dense_ff"]}}, {"type": "attention", "mixer": chk, "mlp": moe},
+             {"type": "attention_2", "mixer": rot, "mlp": moe}, {"type": "attention", "mixer": dict(chk, kv_from=1), "mlp": moe}]
+    return {"architecture": "Zasorax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [kinds[i % 4] for i in range(z["layers"])]}
+
+
 def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
     """Algorithmic work of the named launches of ONE layer at n_tok tokens (context ctx per sequence): {name: (flop, bytes)}."""
     W, H, L = z["width"], z["heads"], ctx
@@ -808,6 +832,32 @@ def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
         # (nominal; the pool has no measured f32 figure).
         f32_tf = 148 * 128 * 2 * 1.965e9 / 1e12
         return {k: max(f / ((f32_tf if k.startswith("linear_recurrence") else tf) * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
+    if arch == "zasorax":
+        D, V, G, c = z["dim"], z["vdim"], z["kv_heads"], z["chunk"]
+        seqs = n_tok if decode else max(1, n_tok // L)
+        # (query, key) pairs per head inside the chunks; cache rows that must come from HBM
+        cpairs = n_tok * (L % c + 1) if decode else seqs * ((L // c) * c * (c + 1) / 2 + (L % c) * (L % c + 1) / 2)
+        ckeys = n_tok * (L % c + 1) if decode else n_tok
+        gemm = lambda n, k: (2 * n_tok * n * k, 2 * n * k + n_tok * (2 * k + 4 * n))
+        qkv = H * D + G * D + G * V
+        out["attention q k v g projection"] = gemm(qkv + H, W)
+        out["attention q k v projection"] = gemm((qkv + H * D) // 2, W)      # the mean of a layer with keys of its own and one without
+        out["attn_rotary_store"] = (0, n_tok * qkv * 6)
+        out["attn_wide_norm_store"] = (0, n_tok * (qkv + H * D) // 2 * 6)
+        out["biased_attention (rotated values)"] = (2 * pairs * H * (D + V), (n_tok * L if decode else n_tok) * G * (D + V) * 2 + n_tok * H * (D + V) * 2)
+        out["biased_attention (chunked)"] = (2 * cpairs * H * (D + V), ckeys * G * (D + V) * 2 + n_tok * H * (D + V) * 2)
+        out["mixer output projection"] = gemm(W, H * V)
+        out["up projection"] = (2 * n_tok * W * z["dense_ff"], 2 * W * z["dense_ff"] + n_tok * 2 * (W + z["dense_ff"]))
+        out["down projection"] = (2 * n_tok * W * z["dense_ff"], 2 * W * z["dense_ff"] + n_tok * 2 * (W + z["dense_ff"]))
+        out["ff_activation (xielu)"] = (0, n_tok * z["dense_ff"] * 4)
+        used = min(z["experts"], n_tok * z["top"])
+        out["expert gate / up grouped GEMM"] = (2 * n_tok * z["top"] * W * 2 * z["ff"], 2 * used * 2 * z["ff"] * W)
+        out["expert down grouped GEMM"] = (2 * n_tok * z["top"] * W * z["ff"], 2 * used * z["ff"] * W)
+        out["ff_activation (silu gate)"] = (0, n_tok * z["top"] * z["ff"] * 6)
+        out["expert row gather"] = (0, n_tok * z["top"] * W * 4)
+        out["moe_combine"] = (0, n_tok * (z["top"] + 1) * W * 2)
+        out["rms_residual_norm"] = (0, n_tok * W * (4 + 4 + 2 + 2))
+        return {k: max(f / (tf * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
     if arch == "zudatar":
         D, V, G, R, QR, w = z["dim"], z["vdim"], z["kv_heads"], z["kv_rank"], z["q_rank"], z["window"]
         dH, dG, dD, dV, lr = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["low_rank"]
@@ -872,7 +922,7 @@ def run_arch_compare(args, new_arch="kosazen"):
     rng = __import__("numpy").random.default_rng(0)
     result = {"workload": f"{new_arch}-vs-qwen3", "data": "synthetic", "dtype": "bf16", "prefill": f"{n_prompts} x {plen} tokens per step",
               "decode": f"{dec_b} sequences at context {plen}+", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf}, "sizes": {}}
-    sizes = {"kosazen": ARCH_SIZES, "talapel": TALAPEL_SIZES, "zudatar": ZUDATAR_SIZES}[new_arch]
+    sizes = {"kosazen": ARCH_SIZES, "talapel": TALAPEL_SIZES, "zudatar": ZUDATAR_SIZES, "zasorax": ZASORAX_SIZES}[new_arch]
     only = os.environ.get("BENCH_ARCH_SIZES")          # e.g. "w2048": a subset of the sizes
     for name, z in sizes.items():
         if only and name not in only.split(","):
@@ -883,6 +933,9 @@ def run_arch_compare(args, new_arch="kosazen"):
         elif new_arch == "zudatar":   # three of four layers have a feed-forward
             z = dict(z, shared_ff=0, top=0, ff=0)
             mlp_q = z["dense_ff"] * 3 // 4 // 64 * 64
+        elif new_arch == "zasorax":   # one dense layer of two matrices, three of `top` gated experts: the mean, as a gated MLP
+            z = dict(z, shared_ff=0)
+            mlp_q = (2 * z["dense_ff"] + 3 * 3 * z["top"] * z["ff"]) // 12 // 64 * 64
         else:
             mlp_q = z["top"] * z["ff"] + z["shared_ff"]
         result["sizes"][name] = {}
@@ -897,6 +950,8 @@ def run_arch_compare(args, new_arch="kosazen"):
                 cfg = E.Config(model_config=talapel_config(z), **common)
             elif arch == "zudatar":
                 cfg = E.Config(model_config=zudatar_config(z), **common)
+            elif arch == "zasorax":
+                cfg = E.Config(model_config=zasorax_config(z), **common)
             else:
                 cfg = E.Config("qwen3-0.6b", vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
                                intermediate_size=mlp_q, num_attention_heads=z["heads"],
@@ -1001,6 +1056,10 @@ def main():
     torch.cuda.set_device(local)
     lib = E.lib()
     assert lib.nvllm_device_ok() == 1, "no sm_100 device: the product path has no fallback"
+    if args.workload == "zasorax":
+        assert world == 1, "--workload zasorax is a one-GPU comparison"
+        print(json.dumps(run_arch_compare(args, "zasorax")), flush=True)
+        return 0
     if args.workload == "zudatar":
         assert world == 1, "--workload zudatar is a one-GPU comparison"
         print(json.dumps(run_arch_compare(args, "zudatar")), flush=True)
