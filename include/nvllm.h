@@ -576,7 +576,7 @@ int nvllm_attn_rotary_store(void* q, int64_t ldq, void* k_cache, void* v_cache, 
 /* nvllm_window_attention with four more options, each off when zero / NULL:
  *   chunk > 0: position p sees only the keys of its own chunk, floor(p / chunk) * chunk .. p (chunks count from position 0);
  *   head_scale (f32 [heads]): the scaled score of head h is multiplied by head_scale[h];
- *   dist_bias (f32 [dist_rows, heads]): dist_bias[min(p - j, dist_rows - 1), h] is added to the score of key j (after scale,
+ *   dist_bias (f32 [heads, dist_rows]): dist_bias[h, min(p - j, dist_rows - 1)] is added to the score of key j (after scale,
  *     temperature and cap; the sink gets none);
  *   out_rot_table (f32 [max_pos, vdim / 2, 2] of (cos, sin), as nvllm_rope_table_interleaved builds for dims = vdim): every
  *     head's output is turned by -p, value m paired with m + vdim / 2, before the gate (values that were stored rotated by

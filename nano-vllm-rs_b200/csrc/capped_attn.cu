@@ -153,6 +153,22 @@ __global__ void __launch_bounds__(128) attn_rope_norm_store_kernel(const RopeSto
     return v;
   };
   float r = 1.0f;
+  if (a.dim <= 512) {   // the head stays in registers: one pass over the projection
+    float keep[16], sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int c = lane + 32 * k;
+      keep[k] = c < a.dim ? value(c) : 0.f;
+      sq = fmaf(keep[k], keep[k], sq);
+    }
+    if (a.norm_eps > 0.f) r = 1.0f / sqrtf(warp_sum(sq) / a.dim + a.norm_eps);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int c = lane + 32 * k;
+      if (c < a.dim) stv(dst + c, keep[k] * r);
+    }
+    return;
+  }
   if (a.norm_eps > 0.f) {
     float sq = 0.f;
     for (int c = lane; c < a.dim; c += 32) { const float v = value(c); sq = fmaf(v, v, sq); }
@@ -223,7 +239,7 @@ struct AttnArgs {
   // positional options of nvllm_biased_attention (all off when zero / null)
   int chunk;                 // > 0: position p sees only the keys of its own chunk, floor(p / chunk) * chunk .. p
   const float* head_scale;   // [heads]: a factor per head on the scaled score
-  const float* dist_bias;    // [dist_rows, heads]: added to the score of key j: dist_bias[min(p - j, dist_rows - 1), h]
+  const float* dist_bias;    // [heads, dist_rows]: added to the score of key j: dist_bias[h, min(p - j, dist_rows - 1)]
   int dist_rows;
   const float2* out_rot;     // [max_pos, vdim / 2] (cos, sin): every head's output is turned by -p, value m paired with m + vdim / 2
   int max_pos;
@@ -276,7 +292,7 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
         float d = 0.f;
         for (int c = 0; c < a.dim; ++c) d = fmaf(qw[c], ldv(kr + c), d);
         s = a.softcap > 0.f ? a.softcap * tanhf(d / a.softcap) : d;
-        if (a.dist_bias) s += a.dist_bias[static_cast<int64_t>(min(nkeys - 1 - j, a.dist_rows - 1)) * a.heads + h];
+        if (a.dist_bias) s += a.dist_bias[static_cast<int64_t>(h) * a.dist_rows + min(nkeys - 1 - j, a.dist_rows - 1)];
       }
     }
     const float mt = warp_max(s);
@@ -363,12 +379,11 @@ __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2
 
 // One warp's share of a key tile: 16 rows x (16 NP) keys -> S on tensor cores, cap / mask / online softmax in f32, then
 // O[:, 0 .. 16 VP) += P . V.  k_addr / v_addr are the warp's ldmatrix lane addresses of its first key (and first value column).
-// bias (EXT): per row, the column of the distance-bias table of the row's head (null: none), rows `heads` apart.
+// bias (EXT): per row, the row of the distance-bias table of the row's head (null: none), one value per distance.
 template <int DMAX, int VMAX, int NP, int VP, int QS, int VS, bool EXT>
 __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2], float (&l)[2], uint32_t q_addr, uint32_t k_addr,
                                           uint32_t v_addr, int key0, const int (&pos)[2], const int (&lo)[2], const float (&qscale)[2],
-                                          bool capped, float cap2, bool need_mask, int tq4, const float* const (&bias)[2], int heads,
-                                          int dist_rows) {
+                                          bool capped, float cap2, bool need_mask, int tq4, const float* const (&bias)[2], int dist_rows) {
   float s[2 * NP][4];
 #pragma unroll
   for (int i = 0; i < 2 * NP; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -392,7 +407,7 @@ __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2]
       const int i = e >> 1, j = key0 + nt * 8 + 2 * tq4 + (e & 1);
       float v = s[nt][e] * qscale[i];            // with a cap: the score over the cap; without: the score in log2 units
       if (capped) v = cap2 * fast_tanh(v);
-      if (EXT) { if (bias[i] != nullptr && j <= pos[i]) v = fmaf(__ldg(bias[i] + min(pos[i] - j, dist_rows - 1) * heads), kLog2e, v); }
+      if (EXT) { if (bias[i] != nullptr && j <= pos[i]) v = fmaf(__ldg(bias[i] + min(pos[i] - j, dist_rows - 1)), kLog2e, v); }
       if (need_mask) v = (j <= pos[i] && j >= lo[i]) ? v : -INFINITY;   // lo: the first key of the row's window or chunk
       s[nt][e] = v;
       mx[i] = fmaxf(mx[i], v);
@@ -516,7 +531,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     if (EXT) {
       const int h = g * group + r % group;
       if (a.head_scale) qscale[i] *= a.head_scale[h];
-      if (a.dist_bias) bias[i] = a.dist_bias + h;
+      if (a.dist_bias) bias[i] = a.dist_bias + static_cast<int64_t>(h) * a.dist_rows;
     }
   }
   // the smallest position of the warp's rows decides whether a tile needs the causal mask (empty rows count as hidden)
@@ -551,15 +566,14 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
       if (key0 < nkeys)
         attn_tile<DMAX, VMAX, 1, VMAX / 32, QS, VS, EXT>(o, m, l, q_addr, smem_u32(kb + kq * 16 * QS + k_lane),
                                                          smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, lo, qscale, capped, cap2,
-                                                         key0 + 15 > min_pos || key0 < max_lo, tq4, bias, a.heads, a.dist_rows);
+                                                         key0 + 15 > min_pos || key0 < max_lo, tq4, bias, a.dist_rows);
     } else if (warp_has_rows) {
       // two halves of 32 keys: half the score registers of a 64-key pass (no spills under the 128-register cap)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf)
         attn_tile<DMAX, VMAX, 2, VMAX / 16, QS, VS, EXT>(o, m, l, q_addr, smem_u32(kb + hf * 32 * QS + k_lane), smem_u32(vb + hf * 32 * VS + v_lane),
                                                          kt * kKeys + hf * 32, pos, lo, qscale, capped, cap2,
-                                                         kt * kKeys + hf * 32 + 31 > min_pos || kt * kKeys + hf * 32 < max_lo, tq4, bias, a.heads,
-                                                         a.dist_rows);
+                                                         kt * kKeys + hf * 32 + 31 > min_pos || kt * kKeys + hf * 32 < max_lo, tq4, bias, a.dist_rows);
     }
     if (tid < kKeys) slot_s[kt & 1][tid] = slot_ahead;   // tile kt's slots were consumed by load_tile(kt) an iteration ago
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it
@@ -588,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     __syncthreads();
     const int rows = ntok * group;
     // with the output rotation a thread merges both values of a pair (c, c + vdim / 2), turns them and stores them
-    const bool rot = EXT && a.out_rot != nullptr;
+    const bool rot = a.out_rot != nullptr;
     const int cols = rot ? a.vdim / 2 : a.vdim;
     for (int e = tid; e < rows * cols; e += kThreads) {
       const int r = e / cols, c = e - r * cols, t = r / group, h = g * group + r % group;
@@ -638,7 +652,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     bf16* op = static_cast<bf16*>(a.out) + static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim;
     const float* gt = a.gate ? a.gate + static_cast<int64_t>(tok0 + t) * a.ldg + (a.gate_per_head ? h : static_cast<int64_t>(h) * a.vdim) : nullptr;
     const float gh = (gt && a.gate_per_head) ? 1.0f / (1.0f + __expf(-gt[0])) : 1.0f;
-    if (EXT && a.out_rot != nullptr) {   // vdim == VMAX here: a thread's columns c and c + VMAX / 2 are both its own
+    if (a.out_rot != nullptr) {   // vdim == VMAX here: a thread's columns c and c + VMAX / 2 are both its own
       const int p = pos[i] >= a.max_pos ? a.max_pos - 1 : pos[i];
       const float4* tab = reinterpret_cast<const float4*>(a.out_rot + static_cast<int64_t>(p) * (VMAX / 2));
 #pragma unroll
@@ -812,8 +826,9 @@ extern "C" int nvllm_biased_attention(void* out, int64_t ldo, const void* q, int
   if (dtype == NVLLM_BF16 && cu_tokens != nullptr && n_seqs > 0 && knobs().capped_mma && group <= kRows && dim % 8 == 0 && vdim % 8 == 0 &&
       dim <= 128 && vdim <= 128 && ldq % 8 == 0 && k_row % 8 == 0 && v_row % 8 == 0 && ldo % 2 == 0 && aligned16(q) && aligned16(k_cache) &&
       aligned16(v_cache) && (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
-    // the positional options live in a second instantiation, so that kernels without them keep their registers
-    const bool ext = head_scale != nullptr || dist_bias != nullptr || out_rot_table != nullptr;
+    // the factor per head and the distance bias live in a second instantiation, so that kernels without them keep their
+    // registers (the output rotation only touches the epilogue)
+    const bool ext = head_scale != nullptr || dist_bias != nullptr;
     const int vmax = vdim <= 64 ? 64 : 128;
     // the output rotation pairs column c with c + vdim / 2 inside one thread's accumulators: vdim must fill the tile
     if (out_rot_table == nullptr || (vdim == vmax && aligned16(out_rot_table))) {

@@ -369,8 +369,8 @@ class Zasorax : public ModelImpl {
     NVLLM_CHECK_ARG(t.kind >= 0, NVLLM_ERR_ARG, "load_weight: unknown tensor '%s'", name_c);
     const uint16_t* src = static_cast<const uint16_t*>(src_v);
     if (t.kind == 2) {
-      // the table as stored is [buckets, heads]; what the kernel reads is one row per distance 0 .. far (every larger
-      // distance reads the last row, and inside a chunk no distance reaches the chunk's size)
+      // the table as stored is [buckets, heads]; what the kernel reads is, per head, one value per distance 0 .. far (every
+      // larger distance reads the last one, and inside a chunk no distance reaches the chunk's size)
       Layer& L = layers_[t.layer];
       NVLLM_CHECK_ARG(rows > 0 && cols == L.H, NVLLM_ERR_ARG, "load_weight(%s): expected [rows, %d], got [%lld, %lld]", name_c, L.H, (long long)rows,
                       (long long)cols);
@@ -380,7 +380,7 @@ class Zasorax : public ModelImpl {
       std::vector<float> ex(static_cast<size_t>(dr) * L.H);
       for (int n = 0; n < dr; ++n) {
         const int b = distance_bucket(n, L.rel_rows, L.bias_max);
-        for (int h = 0; h < L.H; ++h) ex[static_cast<size_t>(n) * L.H + h] = bf16_bits_to_f32(src[static_cast<size_t>(b) * L.H + h]);
+        for (int h = 0; h < L.H; ++h) ex[static_cast<size_t>(h) * dr + n] = bf16_bits_to_f32(src[static_cast<size_t>(b) * L.H + h]);
       }
       if (L.dist == nullptr || dr > L.dist_rows) RUN(dalloc(&L.dist, ex.size()));
       L.dist_rows = dr;

@@ -621,14 +621,14 @@ def attn_rotary_store(proj, heads, kv_heads, dim, vdim, positions, table, rot_di
 
 def biased_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, block_size, heads, kv_heads, dim, vdim, scale, window=0,
                      sinks=None, gate_per_head=False, chunk=0, head_scale=None, dist_bias=None, out_rot=None, cu_tokens=None):
-    """window_attention with a chunk mask, a factor per head, a distance-bias table [rows, heads] and an output rotation table."""
+    """window_attention with a chunk mask, a factor per head, a distance-bias table [heads, rows] and an output rotation table."""
     n = q.shape[0]
     out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
     check(_ffi.lib().nvllm_biased_attention(_p(out), out.stride(0), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                             int(gate_per_head), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(tok_seq),
                                             _p(positions), _p(tables), tables.shape[1] if tables is not None else 1, block_size, n, heads,
                                             kv_heads, dim, vdim, scale, 0.0, 0.0, 1, window, _p(sinks), chunk, _p(head_scale), _p(dist_bias),
-                                            dist_bias.shape[0] if dist_bias is not None else 0, _p(out_rot),
+                                            dist_bias.shape[1] if dist_bias is not None else 0, _p(out_rot),
                                             out_rot.shape[0] if out_rot is not None else 0, _p(cu_tokens),
                                             cu_tokens.shape[0] - 1 if cu_tokens is not None else 0, _dt(q), _stream()))
     return out

@@ -170,7 +170,8 @@ def _paged(rng, ctxs, bs, spare=3):
 
 
 def _attend(q, keys, vals, H, G, scale, pos, chunk=0, sink=None, temp=None, dist=None, gate=None, vrot=None):
-    """One token: q [H, D], keys / vals of positions 0..pos as [pos + 1, G, *].  dist: [rows, H], read at min(distance, rows - 1).
+    """One token: q [H, D], keys / vals of positions 0..pos as [pos + 1, G, *].  dist: [rows, H], read at min(distance, rows - 1)
+    (the kernel takes it per head, [H, rows]).
     vrot = (vdim, base): the values are stored rotated by their position and the output is turned back by -pos."""
     first = pos // chunk * chunk if chunk else 0
     out = []
@@ -217,7 +218,7 @@ def _attention_case(cuda, rng, dtype, H, G, D, V, bs, chunk=0, with_dist=0, rota
     got = ops.biased_attention(dev_t(q.reshape(len(pos), -1), cuda, dtype), dev_t(gt, cuda) if gate else None, kc, vc, dev_i(tok_seq, cuda),
                                dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs, H, G, D, V, scale, sinks=dev_t(sink, cuda),
                                gate_per_head=gate, chunk=chunk, head_scale=dev_t(temp, cuda) if temp is not None else None,
-                               dist_bias=dev_t(dist, cuda) if with_dist else None,
+                               dist_bias=dev_t(dist.T, cuda) if with_dist else None,
                                out_rot=dev_t(rope_np(int(pos.max()) + 5, V, base), cuda) if rotated else None, cu_tokens=dev_i(cu, cuda))
     ref = np.stack([_attend(q[t], keys[tok_seq[t]], vals[tok_seq[t]], H, G, scale, int(pos[t]), chunk, sink, temp, dist,
                             gt[t] if gate else None, (V, base) if rotated else None) for t in range(len(pos))])
@@ -269,7 +270,7 @@ def _standout(cuda, dtype, p, portion, chunk, bs, hot=None, sink=None, dist=None
     sk = np.full(H, sink if sink is not None else -30.0)
     got = ops.biased_attention(dev_t(q.reshape(portion, -1), cuda, dtype), None, kc, vc, dev_i(np.zeros(portion, np.int32), cuda),
                                dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs, H, G, D, V, scale, sinks=dev_t(sk, cuda), chunk=chunk,
-                               dist_bias=dev_t(dist, cuda) if dist is not None else None, cu_tokens=dev_i(np.array([0, portion], np.int32), cuda))
+                               dist_bias=dev_t(dist.T, cuda) if dist is not None else None, cu_tokens=dev_i(np.array([0, portion], np.int32), cuda))
     ref = _attend(q[-1], keys, vals, H, G, scale, p, chunk, sk, None, dist)
     return npf(got)[-1], ref, vals
 
