@@ -83,6 +83,25 @@ struct RopeStoreArgs {
   const float2* vtable;  // non-null: every value head is rotated too, over all of vdim (same pairing), by this table
 };
 
+// A warp's head of up to 32 NK values: computed once (value(c)), kept in registers, divided by its root mean square
+// (eps > 0) and stored.
+template <int NK, typename T, typename F>
+__device__ __forceinline__ void head_norm_store(F value, T* dst, int dim, float eps, int lane) {
+  float keep[NK], sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < NK; ++k) {
+    const int c = lane + 32 * k;
+    keep[k] = c < dim ? value(c) : 0.f;
+    sq = fmaf(keep[k], keep[k], sq);
+  }
+  const float r = eps > 0.f ? 1.0f / sqrtf(warp_sum(sq) / dim + eps) : 1.0f;
+#pragma unroll
+  for (int k = 0; k < NK; ++k) {
+    const int c = lane + 32 * k;
+    if (c < dim) stv(dst + c, keep[k] * r);
+  }
+}
+
 // One warp per (token, head) over the heads [q heads | key heads | value heads].  A query or key head: bias, rotation of the
 // pairs (2i, 2i+1) of its first rot_dims values by position * base^(-2i/rot_dims), then (norm_eps > 0) division by the root
 // mean square of the whole head; queries go to q, keys to their cache row.  A value head: bias, then its cache row; with
@@ -153,22 +172,11 @@ __global__ void __launch_bounds__(128) attn_rope_norm_store_kernel(const RopeSto
     return v;
   };
   float r = 1.0f;
-  if (a.dim <= 512) {   // the head stays in registers: one pass over the projection
-    float keep[16], sq = 0.f;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const int c = lane + 32 * k;
-      keep[k] = c < a.dim ? value(c) : 0.f;
-      sq = fmaf(keep[k], keep[k], sq);
-    }
-    if (a.norm_eps > 0.f) r = 1.0f / sqrtf(warp_sum(sq) / a.dim + a.norm_eps);
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const int c = lane + 32 * k;
-      if (c < a.dim) stv(dst + c, keep[k] * r);
-    }
-    return;
-  }
+  // heads of up to 512 values stay in registers (one pass over the projection), in the smallest unrolled size that holds them
+  if (a.dim <= 64) { head_norm_store<2>(value, dst, a.dim, a.norm_eps, lane); return; }
+  if (a.dim <= 128) { head_norm_store<4>(value, dst, a.dim, a.norm_eps, lane); return; }
+  if (a.dim <= 256) { head_norm_store<8>(value, dst, a.dim, a.norm_eps, lane); return; }
+  if (a.dim <= 512) { head_norm_store<16>(value, dst, a.dim, a.norm_eps, lane); return; }
   if (a.norm_eps > 0.f) {
     float sq = 0.f;
     for (int c = lane; c < a.dim; c += 32) { const float v = value(c); sq = fmaf(v, v, sq); }
@@ -243,7 +251,11 @@ struct AttnArgs {
   int dist_rows;
   const float2* out_rot;     // [max_pos, vdim / 2] (cos, sin): every head's output is turned by -p, value m paired with m + vdim / 2
   int max_pos;
+  int bias_staged;           // tensor-core kernel: the CTA copies its heads' rows of dist_bias into shared memory first
 };
+
+// shared memory the tensor-core kernel may spend on the distance-bias rows of a CTA's heads (two CTAs per SM still fit)
+constexpr int kBiasSmemBytes = 9216;
 
 // first key a row at position p sees
 __device__ __forceinline__ int first_key(const AttnArgs& a, int p) {
@@ -407,7 +419,7 @@ __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2]
       const int i = e >> 1, j = key0 + nt * 8 + 2 * tq4 + (e & 1);
       float v = s[nt][e] * qscale[i];            // with a cap: the score over the cap; without: the score in log2 units
       if (capped) v = cap2 * fast_tanh(v);
-      if (EXT) { if (bias[i] != nullptr && j <= pos[i]) v = fmaf(__ldg(bias[i] + min(pos[i] - j, dist_rows - 1)), kLog2e, v); }
+      if (EXT) { if (bias[i] != nullptr && j <= pos[i]) v = fmaf(bias[i][min(pos[i] - j, dist_rows - 1)], kLog2e, v); }
       if (need_mask) v = (j <= pos[i] && j >= lo[i]) ? v : -INFINITY;   // lo: the first key of the row's window or chunk
       s[nt][e] = v;
       mx[i] = fmaxf(mx[i], v);
@@ -481,6 +493,11 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   const bf16* vc = static_cast<const bf16*>(a.vc) + static_cast<int64_t>(g) * a.vdim;
   // zero everything once (padding columns and rows stay zero), then the query rows
   for (int i = tid; i < (kRows * QS + 2 * kKeys * QS + 2 * kKeys * VS) / 8; i += kThreads) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
+  // the distance-bias rows of this CTA's heads (consecutive rows of the table), behind the tiles: one shared-memory load per
+  // score instead of a global one
+  float* bias_s = reinterpret_cast<float*>(smem_raw + static_cast<size_t>(kRows * QS + 2 * kKeys * QS + 2 * kKeys * VS) * sizeof(bf16));
+  if (EXT && a.bias_staged)
+    for (int i = tid; i < group * a.dist_rows; i += kThreads) bias_s[i] = a.dist_bias[static_cast<int64_t>(g) * group * a.dist_rows + i];
   __syncthreads();
   const int dch = a.dim / 8, vch = a.vdim / 8;     // 16-byte chunks per row
   // the query rows travel with the first key tile's copy group (asynchronous: no thread waits for its own row here)
@@ -531,7 +548,7 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     if (EXT) {
       const int h = g * group + r % group;
       if (a.head_scale) qscale[i] *= a.head_scale[h];
-      if (a.dist_bias) bias[i] = a.dist_bias + static_cast<int64_t>(h) * a.dist_rows;
+      if (a.dist_bias) bias[i] = a.bias_staged ? bias_s + (r % group) * a.dist_rows : a.dist_bias + static_cast<int64_t>(h) * a.dist_rows;
     }
   }
   // the smallest position of the warp's rows decides whether a tile needs the causal mask (empty rows count as hidden)
@@ -675,10 +692,13 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
 }
 
 template <int DMAX, int VMAX, bool EXT>
-int launch_mma(const AttnArgs& a, const int32_t* cu_tokens, int n_seqs, cudaStream_t st) {
+int launch_mma(AttnArgs a, const int32_t* cu_tokens, int n_seqs, cudaStream_t st) {
   const int group = a.heads / a.kv_heads, tq = kRows / group;
-  const size_t smem = (static_cast<size_t>(kRows) * (DMAX + 8) + 2 * kKeys * (DMAX + 8) + 2 * kKeys * (VMAX + 8)) * sizeof(bf16);
-  NVLLM_SMEM_ATTR_ONCE((capped_attn_mma_kernel<DMAX, VMAX, EXT>), smem);
+  const size_t tiles = (static_cast<size_t>(kRows) * (DMAX + 8) + 2 * kKeys * (DMAX + 8) + 2 * kKeys * (VMAX + 8)) * sizeof(bf16);
+  const size_t bias_bytes = static_cast<size_t>(group) * a.dist_rows * sizeof(float);
+  a.bias_staged = EXT && a.dist_bias != nullptr && bias_bytes <= kBiasSmemBytes;
+  const size_t smem = tiles + (a.bias_staged ? bias_bytes : 0);
+  NVLLM_SMEM_ATTR_ONCE((capped_attn_mma_kernel<DMAX, VMAX, EXT>), tiles + (EXT ? kBiasSmemBytes : 0));
   dim3 grid((a.n + tq - 1) / tq + n_seqs, a.kv_heads);
   capped_attn_mma_kernel<DMAX, VMAX, EXT><<<grid, kThreads, smem, st>>>(a, cu_tokens, n_seqs, tq, group);
   NVLLM_LAUNCH_CHECK("capped_attn_mma_kernel");
@@ -819,7 +839,7 @@ extern "C" int nvllm_biased_attention(void* out, int64_t ldo, const void* q, int
   NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && (block_tables || cu_tokens), NVLLM_ERR_ARG, "attention: NULL");
   AttnArgs a{out, ldo, q, ldq, gate, ldg, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables, table_cap, block_size,
              n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every, window > 0 ? window : 0, sinks, gate_per_head, block_tables ? nullptr : cu_tokens,
-             chunk, head_scale, dist_bias, dist_rows, reinterpret_cast<const float2*>(out_rot_table), max_pos};
+             chunk, head_scale, dist_bias, dist_rows, reinterpret_cast<const float2*>(out_rot_table), max_pos, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 with 16-byte rows and a token range per sequence: tensor cores; everything else (f32, odd sizes): one warp per row
   const int group = heads / kv_heads;
