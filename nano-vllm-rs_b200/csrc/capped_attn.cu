@@ -234,6 +234,63 @@ __global__ void __launch_bounds__(128) attn_rope_norm_store_vec_kernel(const Rop
   }
 }
 
+// The halves pairing with 16-byte accesses: no biases, heads of 4 .. 512 values whose rotated part (and vdim, when the values
+// are rotated) is a multiple of 8, aligned rows.  A lane owns chunks of 4 neighbouring values; the partner of a chunk in the
+// rotation is the chunk half the rotated part away (read again: it is in L1), so nothing crosses lanes but the norm's sum.
+template <typename T>
+__global__ void __launch_bounds__(128) attn_rotary_store_halves_vec_kernel(const RopeStoreArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = a.heads + 2 * a.kv_heads;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  if (item >= static_cast<int64_t>(a.n) * per) return;
+  const int t = static_cast<int>(item / per), hh = static_cast<int>(item % per);
+  const int32_t slot = a.slots[t];
+  const bool is_q = hh < a.heads, is_v = hh >= a.heads + a.kv_heads;
+  if (!is_q && slot < 0) return;
+  const int h = is_q ? hh : (is_v ? hh - a.heads - a.kv_heads : hh - a.heads);
+  const int qn = a.heads * a.dim, kn = a.kv_heads * a.dim;
+  const int size = is_v ? a.vdim : a.dim, rot = is_v ? (a.vtable ? a.vdim : 0) : a.rot_dims, hr4 = rot / 8;   // chunks in half the rotated part
+  const float4* src = reinterpret_cast<const float4*>(a.proj + static_cast<int64_t>(t) * a.ldp + (is_q ? 0 : (is_v ? qn + kn : qn)) +
+                                                      static_cast<int64_t>(h) * size);
+  int64_t pos = a.positions[t];
+  pos = pos < 0 ? 0 : (pos >= a.max_pos ? a.max_pos - 1 : pos);
+  const float4* tab = reinterpret_cast<const float4*>((is_v ? a.vtable : a.table) + pos * (rot / 2));   // (cos, sin) of two pairs per float4
+  T* dst = is_q ? static_cast<T*>(a.q) + static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(h) * size
+                : (is_v ? static_cast<T*>(a.vc) + static_cast<int64_t>(slot) * a.v_row + static_cast<int64_t>(h) * size
+                        : static_cast<T*>(a.kc) + static_cast<int64_t>(slot) * a.k_row + static_cast<int64_t>(h) * size);
+  const int nv = size / 4;
+  float4 v[4];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < nv) {
+      float4 x = src[c];
+      if (c < 2 * hr4) {
+        const bool second = c >= hr4;
+        const float4 o = src[second ? c - hr4 : c + hr4];
+        const int m = second ? c - hr4 : c;
+        const float4 cs0 = tab[2 * m], cs1 = tab[2 * m + 1];
+        const float sg = second ? 1.0f : -1.0f;                 // (u cos - v sin, v cos + u sin)
+        x.x = fmaf(x.x, cs0.x, sg * o.x * cs0.y); x.y = fmaf(x.y, cs0.z, sg * o.y * cs0.w);
+        x.z = fmaf(x.z, cs1.x, sg * o.z * cs1.y); x.w = fmaf(x.w, cs1.z, sg * o.w * cs1.w);
+      }
+      v[k] = x;
+      sq += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  const float r = (!is_v && a.norm_eps > 0.f) ? 1.0f / sqrtf(warp_sum(sq) / size + a.norm_eps) : 1.0f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < nv) {
+      const float4 o = make_float4(v[k].x * r, v[k].y * r, v[k].z * r, v[k].w * r);
+      if (sizeof(T) == 2) *reinterpret_cast<uint2*>(dst + 4 * c) = make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
+      else *reinterpret_cast<float4*>(dst + 4 * c) = o;
+    }
+  }
+}
+
 struct AttnArgs {
   void* out; int64_t ldo;
   const void* q; int64_t ldq;
@@ -790,6 +847,15 @@ extern "C" int nvllm_attn_rotary_store(void* q, int64_t ldq, void* k_cache, void
     if (dtype == NVLLM_BF16) attn_rope_norm_store_vec_kernel<bf16><<<static_cast<unsigned>((vitems + 3) / 4), 128, 0, st>>>(a);
     else attn_rope_norm_store_vec_kernel<float><<<static_cast<unsigned>((vitems + 3) / 4), 128, 0, st>>>(a);
     NVLLM_LAUNCH_CHECK("attn_rope_norm_store_vec_kernel");
+    return 0;
+  }
+  // halves pairing, no biases, values of their own, 16-byte rows and rotated parts that split into chunks of 4: the vector kernel
+  if (halves && !v_from_k && !q_bias && !k_bias && !v_bias && dim % 4 == 0 && vdim % 4 == 0 && dim <= 512 && vdim <= 512 && rot_dims % 8 == 0 &&
+      (v_rope_table == nullptr || vdim % 8 == 0) && ldp % 4 == 0 && ldq % 4 == 0 && k_row % 4 == 0 && v_row % 4 == 0 && aligned16(proj) && aligned16(q) &&
+      aligned16(k_cache) && aligned16(v_cache) && aligned16(rope_table) && aligned16(v_rope_table)) {
+    if (dtype == NVLLM_BF16) attn_rotary_store_halves_vec_kernel<bf16><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);
+    else attn_rotary_store_halves_vec_kernel<float><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);
+    NVLLM_LAUNCH_CHECK("attn_rotary_store_halves_vec_kernel");
     return 0;
   }
   if (dtype == NVLLM_BF16) attn_rope_norm_store_kernel<bf16><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(a);

@@ -130,7 +130,8 @@ def test_norm_over_the_whole_projection_and_store(cuda, dtype, H, G, D, V, own):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,V,rot", [(4, 2, 8, 6, 4), (2, 1, 64, 64, 64), (3, 3, 10, 4, 0), (1, 1, 2, 2, 2), (5, 5, 12, 20, 6)])
+@pytest.mark.parametrize("H,G,D,V,rot", [(4, 2, 8, 6, 4), (2, 1, 64, 64, 64), (3, 3, 10, 4, 0), (1, 1, 2, 2, 2), (5, 5, 12, 20, 6),
+                                         (4, 2, 128, 128, 64), (2, 2, 32, 16, 16), (3, 1, 24, 8, 8), (2, 1, 512, 256, 128), (3, 3, 12, 8, 0)])
 def test_rotary_halves_norm_and_rotated_values_store(cuda, dtype, H, G, D, V, rot):
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(H * 10 + D + rot)
