@@ -105,7 +105,7 @@ def test_post_norm_residual_add(cuda, dtype, hid):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,V,own", [(4, 2, 6, 5, True), (8, 1, 96, 64, True), (3, 3, 10, 10, False), (1, 1, 1, 1, True)])
+@pytest.mark.parametrize("H,G,D,V,own", [(4, 2, 6, 5, True), (6, 1, 80, 48, True), (3, 3, 10, 10, False), (1, 1, 1, 1, True)])
 def test_norm_over_the_whole_projection_and_store(cuda, dtype, H, G, D, V, own):
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(H * 100 + D)
@@ -227,7 +227,7 @@ def _attention_case(cuda, rng, dtype, H, G, D, V, bs, chunk=0, with_dist=0, rota
 
 
 CHUNK_CASES = [  # heads, kv heads, dim, vdim, chunk, page, rows of the distance table
-    (4, 2, 6, 5, 7, 16, 5), (8, 1, 96, 64, 64, 64, 64), (4, 2, 64, 64, 33, 16, 300), (2, 2, 128, 128, 70, 32, 20), (3, 1, 16, 8, 1, 16, 1),
+    (4, 2, 6, 5, 7, 16, 5), (12, 2, 80, 64, 48, 32, 48), (4, 2, 64, 64, 33, 16, 300), (2, 2, 128, 128, 70, 32, 20), (3, 1, 16, 8, 1, 16, 1),
     (6, 3, 32, 32, 64, 16, 10), (2, 1, 8, 24, 0, 16, 200), (16, 2, 64, 32, 50, 64, 50),
     (4, 1, 64, 64, 0, 16, 700),   # a table too large for the tensor-core kernel's shared memory: read from global memory
 ]
@@ -243,7 +243,7 @@ def test_chunked_attention_with_distance_bias_temperature_and_sink(cuda, dtype, 
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,V,bs", [(4, 2, 8, 6, 16), (4, 2, 64, 64, 64), (2, 1, 128, 128, 16), (3, 3, 16, 40, 32), (8, 2, 96, 64, 16), (1, 1, 2, 2, 16)])
+@pytest.mark.parametrize("H,G,D,V,bs", [(4, 2, 8, 6, 16), (6, 3, 64, 64, 64), (2, 1, 128, 128, 16), (3, 3, 16, 40, 32), (8, 2, 96, 64, 16), (1, 1, 2, 2, 16)])
 def test_attention_over_rotated_values_turns_the_output_back(cuda, dtype, H, G, D, V, bs):
     got, ref = _attention_case(cuda, np.random.default_rng(H + D + V), dtype, H, G, D, V, bs, rotated=True, gate=True)
     tol = 2e-5 if dtype == F32 else 2e-2
@@ -302,6 +302,8 @@ def test_sink_and_far_distance_bias_stand_out(cuda, dtype, portion):
     assert np.abs(got).max() < 1e-6 and np.abs(ref).max() < 1e-6
     got, ref, _ = _standout(cuda, dtype, 100, portion, 0, 16, hot=3, sink=0.0)    # a key 97 tokens back against a sink of score 0
     assert np.abs(got - ref).max() < tol
+    got, ref, vals = _standout(cuda, dtype, 900, portion, 0, 64, hot=5)            # one key among hundreds, 895 tokens and 13 pages back
+    assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[5, 0]).max() < tol
     dist = np.zeros((90, 2)); dist[77] = 50.0                                      # one distance stands out: key 100 - 77
     got, ref, vals = _standout(cuda, dtype, 100, portion, 0, 16, dist=dist)
     assert np.abs(got - ref).max() < tol and np.abs(got.reshape(2, -1) - vals[23, 0]).max() < tol
@@ -381,11 +383,11 @@ def variant(name):
                               ("attention", C(heads=2, kv_heads=2, dim=8, vdim=8, chunk=1000, scale=1.0, bias_max=2000), Z.dense_mlp(1)),
                               ("attention_2", R(heads=3, kv_heads=3, dim=8, vdim=8, rot_dims=8, rot_base=1.0), Z.expert_mlp(ff=8, experts=2, top=2))],
                              width=16, vocab=33, embed_scale=1.0), {0: 2, 2: 6}
-    if name == "tensor_core":    # sizes the tensor-core kernels accept (bf16): width and inner sizes multiples of 64, heads of 64 / 96 / 128
-        return Z.make_config([("attention_2", R(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=32, rot_base=1e4, scale=0.1), Z.expert_mlp(ff=64, experts=4, top=2)),
-                              ("attention", C(heads=4, kv_heads=1, dim=96, vdim=64, chunk=64, scale=0.1, bias_max=100), Z.dense_mlp(128)),
+    if name == "tensor_core":    # sizes the tensor-core kernels accept (bf16): width and inner sizes multiples of 64, heads of 64 / 80 / 128
+        return Z.make_config([("attention_2", R(heads=6, kv_heads=3, dim=64, vdim=64, rot_dims=32, rot_base=1e4, scale=0.1), Z.expert_mlp(ff=64, experts=4, top=2)),
+                              ("attention", C(heads=4, kv_heads=2, dim=80, vdim=64, chunk=48, scale=0.1, bias_max=100), Z.dense_mlp(128)),
                               ("attention_2", R(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=128, rot_base=500.0, scale=0.09), None),
-                              ("attention", C(heads=2, kv_heads=1, dim=96, vdim=64, chunk=40, scale=0.1, bias_max=30, kv_from=1), Z.expert_mlp(ff=128, experts=3, top=1))],
+                              ("attention", C(heads=2, kv_heads=2, dim=80, vdim=64, chunk=40, scale=0.1, bias_max=30, kv_from=1), Z.expert_mlp(ff=128, experts=3, top=1))],
                              width=64, vocab=96), {1: 16, 3: 10}
     raise KeyError(name)
 
