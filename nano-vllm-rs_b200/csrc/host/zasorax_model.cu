@@ -12,8 +12,8 @@
 //                  the cache rows layer j wrote, with queries, table, temperatures and sinks of its own.
 //   "attention_2"  rotary on the first rot.dims values of every query and key head (value i paired with i + dims / 2), then a
 //                  weightless RMS norm per head; the VALUES are rotated by their position over all of vdim before they are
-//                  cached, and every head's output is turned back by the query's position; causal; softmax with 1 added to
-//                  the denominator (a sink of score 0); one sigmoid gate per head.
+//                  cached, and every head's output is turned back by the query's position; causal; softmax denominator
+//                  1 + sum over the keys (a zero sink); one sigmoid gate per head.
 // Feed-forward: dense, W_down xielu(W_up x) with two learned numbers; or a mixture of experts routed on the logits
 // (z = W_r x + b in f32, the `top` largest, softmax over the chosen alone), experts SiLU-gated.
 // Every size, constant and the layer order come from the configuration; the rows of a distance table come from its tensor.

@@ -16,7 +16,7 @@ Notation: W x for a weight stored [out, in]; positions start at 0 in every seque
   attention_2: q, k, v = Wq x, Wk x, Wv x; rotary on the first rot.dims values of every q and k head (value i paired with
                i + dims / 2, angle pos * base^(-2i / dims)), then each head divided by its root mean square; the value of
                position j turned by j over all of vdim (pair m with m + vdim / 2, angle j * base^(-2m / vdim)) and cached
-               so; s = q.k * scale, causal; softmax with 1 added to the denominator; the head's output turned back by -i;
+               so; s = q.k * scale, causal; p_j = exp(s_j) / (1 + sum_j exp(s_j)); the head's output turned back by -i;
                times sigmoid(Wg x)_head; Wo
   ff dense:    Wd act(Wu x), act(z) = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 else
   ff experts:  z = Wr x + b; the `top` largest z (ties: lowest index) with weights softmax over those alone;

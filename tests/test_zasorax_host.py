@@ -55,7 +55,7 @@ def test_sink_takes_mass_but_gives_nothing():
     s = np.array([0.3, -1.0, 2.0])
     p = Z.sink_softmax(s, 1.0)
     np.testing.assert_allclose(p.sum(), 1.0 - np.exp(1.0) / (np.exp(s).sum() + np.exp(1.0)))
-    np.testing.assert_allclose(Z.sink_softmax(s, 0.0), np.exp(s) / (1.0 + np.exp(s).sum()))     # "one added to the denominator"
+    np.testing.assert_allclose(Z.sink_softmax(s, 0.0), np.exp(s) / (1.0 + np.exp(s).sum()))     # a sink of score 0: 1 + sum in the denominator
     np.testing.assert_allclose(Z.sink_softmax(s, -1e9).sum(), 1.0)
 
 
