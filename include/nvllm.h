@@ -592,6 +592,10 @@ int nvllm_biased_attention(void* out, int64_t ldo, const void* q, int64_t ldq, c
  *   z > 0: softplus(p0) z^2 + z / 2;   z <= 0: (1/2 + softplus(p1)) (exp(z) - 1 - z) + z / 2.   kinds 0 / 1 ignore params. */
 int nvllm_ff_activation_params(void* out, const void* in, int32_t n, int32_t ff, int32_t kind, const float* params, int32_t dtype,
                                void* stream);
+/* h[i, :] = table[ids[i], :] * scale as f32 and x[i, :] = the same row in x_dtype (ids clamped to the table): the stream and
+ * what the first sublayer of a block without an input norm reads, in one pass. */
+int nvllm_embedding_stream(float* h, void* x, int32_t x_dtype, const void* table, const int64_t* ids, int32_t n, int32_t hidden,
+                           int32_t vocab, float scale, int32_t table_dtype, void* stream);
 /* Routing on the logits: z = logits + bias (bias nullable); chosen = the `top` largest z (ties: lowest index);
  * topk_w = softmax over the chosen z alone.  logits: f32 [n, experts] with rows ld apart, experts <= 3072.
  * (nvllm_linear_grouped with glu == 3 is the expert product with the plain gate silu(g) * u.) */

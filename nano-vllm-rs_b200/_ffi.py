@@ -118,6 +118,7 @@ PROTOTYPES = {
     "nvllm_biased_attention": (i32, [vp, i64, vp, i64, vp, i64, i32, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                      f32, f32, f32, i32, i32, vp, i32, vp, vp, i32, vp, i32, vp, i32, i32, vp]),
     "nvllm_ff_activation_params": (i32, [vp, vp, i32, i32, i32, vp, i32, vp]),
+    "nvllm_embedding_stream": (i32, [vp, vp, i32, vp, vp, i32, i32, i32, f32, i32, vp]),
     "nvllm_moe_route_logits": (i32, [vp, vp, vp, i64, vp, i32, i32, i32, vp]),
     "nvllm_latent_window_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp, i64, i32, i32, i32, i32, i32, f32, i32,
                                             vp, vp, i64, vp, sz, i32, vp]),

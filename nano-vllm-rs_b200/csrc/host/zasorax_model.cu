@@ -465,8 +465,7 @@ class Zasorax : public ModelImpl {
       return rc;
     };
     const float norm_eps = eps_ > 0.f ? eps_ : 1e-30f;
-    RUN(nvllm_embedding_gather_scaled(h_, nullptr, embed_, v.ids, N, W, vocab_, embed_scale_, dt_, st)); ++launches; mk("embedding_gather_scaled");
-    RUN(add(nullptr, nullptr, nullptr));
+    RUN(nvllm_embedding_stream(h_, x_, dt_, embed_, v.ids, N, W, vocab_, embed_scale_, dt_, st)); ++launches; mk("embedding_stream");
     for (size_t i = 0; i < layers_.size(); ++i) {
       const Layer& L = layers_[i];
       const LayerCache& kv = L.own_kv() ? cache_[i] : cache_[L.kv_from];

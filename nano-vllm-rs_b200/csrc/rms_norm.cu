@@ -7,6 +7,7 @@
 //                             the row, as nvllm_dyt_residual_norm does for Dynamic Tanh models)
 //   nvllm_rms_norm_rows       rows of an f32 matrix, RMS-normed and weighted, written in the operand type to rows of a
 //                             destination chosen by a map (a paged cache's slots) or in place of order
+//   nvllm_embedding_stream    h[t] = table[id_t] * scale as f32 and, in the same pass, in the operand type
 //   nvllm_embedding_bigram    h[t] = table[id_t] * scale + bigram[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]; the first
 //                             token of a sequence reads the extra row `buckets`.  The token before a portion's first one is
 //                             part of the sequence's state (one int32 per state slot).
@@ -202,6 +203,41 @@ __global__ void __launch_bounds__(128) embedding_bigram_kernel(const BigramArgs 
   }
 }
 
+
+// h[t, :] = table[ids[t], :] * scale as f32, and the same row in the operand type (what the first sublayer of a block without an
+// input norm reads).  CTA per token; bf16 tables with rows of 16-byte multiples move 8 values per access.
+template <typename TT, typename TO>
+__global__ void __launch_bounds__(256) embedding_stream_kernel(float* __restrict__ h, TO* __restrict__ x, const TT* __restrict__ table,
+                                                               const int64_t* __restrict__ ids, int hidden, int vocab, float scale, int vec) {
+  const int64_t t = blockIdx.x;
+  int64_t id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const TT* row = table + id * hidden;
+  float* hr = h + t * hidden;
+  TO* xr = x + t * hidden;
+  if (vec) {   // TT is bf16 here
+    for (int c = threadIdx.x; c < hidden / 8; c += 256) {
+      const uint4 u = ld_nc_16(reinterpret_cast<const uint4*>(row) + c);
+      const float4 a = make_float4(bf16_lo(u.x) * scale, bf16_hi(u.x) * scale, bf16_lo(u.y) * scale, bf16_hi(u.y) * scale);
+      const float4 b = make_float4(bf16_lo(u.z) * scale, bf16_hi(u.z) * scale, bf16_lo(u.w) * scale, bf16_hi(u.w) * scale);
+      reinterpret_cast<float4*>(hr)[2 * c] = a;
+      reinterpret_cast<float4*>(hr)[2 * c + 1] = b;
+      if (sizeof(TO) == 2) {
+        reinterpret_cast<uint4*>(xr)[c] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+      } else {
+        reinterpret_cast<float4*>(xr)[2 * c] = a;
+        reinterpret_cast<float4*>(xr)[2 * c + 1] = b;
+      }
+    }
+    return;
+  }
+  for (int c = threadIdx.x; c < hidden; c += 256) {
+    const float v = (sizeof(TT) == 2 ? __bfloat162float(reinterpret_cast<const bf16*>(row)[c]) : reinterpret_cast<const float*>(row)[c]) * scale;
+    hr[c] = v;
+    st_as(xr, c, v);
+  }
+}
+
 }  // namespace
 }  // namespace nvllm
 
@@ -246,6 +282,27 @@ extern "C" int nvllm_rms_norm_rows(void* out, int64_t ldo, const float* x, int64
   if (out_dtype == NVLLM_BF16) rms_norm_rows_kernel<bf16><<<(n + 3) / 4, 128, 0, st>>>(static_cast<bf16*>(out), ldo, x, ldx, w, row_map, n, cols, eps);
   else rms_norm_rows_kernel<float><<<(n + 3) / 4, 128, 0, st>>>(static_cast<float*>(out), ldo, x, ldx, w, row_map, n, cols, eps);
   NVLLM_LAUNCH_CHECK("rms_norm_rows_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_embedding_stream(float* h, void* x, int32_t x_dtype, const void* table, const int64_t* ids, int32_t n, int32_t hidden,
+                                      int32_t vocab, float scale, int32_t table_dtype, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && hidden > 0 && vocab > 0, NVLLM_ERR_ARG, "embedding_stream: sizes");
+  NVLLM_CHECK_ARG((table_dtype == NVLLM_BF16 || table_dtype == NVLLM_F32) && (x_dtype == NVLLM_BF16 || x_dtype == NVLLM_F32), NVLLM_ERR_DTYPE,
+                  "embedding_stream: dtype %d / %d", table_dtype, x_dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(h && x && table && ids, NVLLM_ERR_ARG, "embedding_stream: NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int vec = table_dtype == NVLLM_BF16 && hidden % 8 == 0 && aligned16(h) && aligned16(x) && aligned16(table);
+  if (table_dtype == NVLLM_BF16 && x_dtype == NVLLM_BF16)
+    embedding_stream_kernel<bf16, bf16><<<n, 256, 0, st>>>(h, static_cast<bf16*>(x), static_cast<const bf16*>(table), ids, hidden, vocab, scale, vec);
+  else if (table_dtype == NVLLM_BF16)
+    embedding_stream_kernel<bf16, float><<<n, 256, 0, st>>>(h, static_cast<float*>(x), static_cast<const bf16*>(table), ids, hidden, vocab, scale, vec);
+  else if (x_dtype == NVLLM_BF16)
+    embedding_stream_kernel<float, bf16><<<n, 256, 0, st>>>(h, static_cast<bf16*>(x), static_cast<const float*>(table), ids, hidden, vocab, scale, 0);
+  else
+    embedding_stream_kernel<float, float><<<n, 256, 0, st>>>(h, static_cast<float*>(x), static_cast<const float*>(table), ids, hidden, vocab, scale, 0);
+  NVLLM_LAUNCH_CHECK("embedding_stream_kernel");
   return 0;
 }
 

@@ -649,3 +649,13 @@ def moe_route_logits(logits, bias, top):
     w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     check(_ffi.lib().nvllm_moe_route_logits(_p(idx), _p(w), _p(logits), logits.stride(0), _p(bias), n, experts, top, _stream()))
     return idx, w
+
+
+def embedding_stream(table, ids, scale, dtype):
+    """table[ids] * scale as the f32 stream, and the same rows in `dtype`."""
+    n, hidden = ids.shape[0], table.shape[1]
+    h = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    x = torch.empty((n, hidden), dtype=dtype, device=table.device)
+    check(_ffi.lib().nvllm_embedding_stream(_p(h), _p(x), BF16 if dtype == torch.bfloat16 else F32, _p(table), _p(ids), n, hidden, table.shape[0],
+                                            float(scale), _dt(table), _stream()))
+    return h, x

@@ -105,6 +105,19 @@ def test_post_norm_residual_add(cuda, dtype, hid):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hid", [24, 7, 320])
+def test_scaled_embedding_as_stream_and_operand(cuda, dtype, hid):
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(hid)
+    table = Z.bf16_round(rng.standard_normal((40, hid)))
+    ids = rng.integers(0, 40, 19)
+    h, x = ops.embedding_stream(dev_t(table, cuda, dtype), dev_i(ids, cuda, torch.int64), 3.7, dtype)
+    ref = f32r(f32r(table[ids]) * np.float32(3.7))
+    np.testing.assert_allclose(npf(h), ref, rtol=1e-6, atol=0)
+    np.testing.assert_array_equal(npf(x), npf(h.to(dtype)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,V,own", [(4, 2, 6, 5, True), (6, 1, 80, 48, True), (3, 3, 10, 10, False), (1, 1, 1, 1, True)])
 def test_norm_over_the_whole_projection_and_store(cuda, dtype, H, G, D, V, own):
     from nano_vllm_rs_b200 import ops
