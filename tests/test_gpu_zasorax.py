@@ -402,10 +402,16 @@ def variant(name):
                               ("attention_2", R(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=128, rot_base=500.0, scale=0.09), None),
                               ("attention", C(heads=2, kv_heads=2, dim=80, vdim=64, chunk=40, scale=0.1, bias_max=30, kv_from=1), Z.expert_mlp(ff=128, experts=3, top=1))],
                              width=64, vocab=96), {1: 16, 3: 10}
+    if name == "mid":            # sizes between: heads of 48 and 32, a width that is no power of two, experts on both grouped kernels
+        return Z.make_config([("attention", C(heads=6, kv_heads=3, dim=48, vdim=32, chunk=100, scale=0.15, bias_max=300), Z.expert_mlp(ff=96, experts=6, top=3)),
+                              ("attention", C(heads=6, kv_heads=3, dim=48, vdim=32, chunk=37, scale=0.15, bias_max=50, kv_from=0), None),
+                              ("attention_2", R(heads=4, kv_heads=4, dim=48, vdim=64, rot_dims=24, rot_base=5e5, scale=0.14), Z.dense_mlp(160)),
+                              ("attention_2", R(heads=8, kv_heads=2, dim=32, vdim=32, rot_dims=32, rot_base=1e4, scale=0.18), Z.expert_mlp(ff=64, experts=3, top=2))],
+                             width=192, vocab=200, embed_scale=5.0), {0: 20, 1: 14}
     raise KeyError(name)
 
 
-VARIANTS = ["all_kinds", "ones", "tensor_core"]
+VARIANTS = ["all_kinds", "ones", "tensor_core", "mid"]
 
 
 def model_for(name, rng):
